@@ -1,0 +1,87 @@
+/* C ABI of the B200 (sm_100a) INT8 SageAttention path.
+ *
+ * This is the drop-in boundary under the `torch.ops.sageattention.*` operators of
+ * LuXuxue/sageattention-rdna3: each entry point below replaces one launcher declared in the
+ * reference's csrc/attn_gfx11.h and takes plain device pointers, sizes and element strides.
+ * All pointers are device pointers on the CURRENT CUDA device unless stated otherwise; all work is
+ * enqueued on `stream` (a cudaStream_t passed as void*) and nothing synchronises.
+ *
+ * Tensors in the caller's layout are described by `sage_strided_t`: a base pointer and the
+ * element strides of the batch, head and sequence dimensions; head_dim is contiguous.  For the
+ * reference's layouts, with x of shape [B,H,S,D] ("HND") pass (x.stride(0), x.stride(1),
+ * x.stride(2)); with [B,S,H,D] ("NHD") pass (x.stride(0), x.stride(2), x.stride(1)).
+ * Base pointers must be 16-byte aligned and strides multiples of 8 elements (16-byte vector
+ * access, as the reference's kernels assume).
+ *
+ * Return value: 0 on success, a SAGE_ERR_* code otherwise; sage_last_error() describes the last
+ * failure of the calling thread.
+ */
+#ifndef SAGE_B200_H_
+#define SAGE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAGE_ABI_VERSION 1
+
+#define SAGE_DTYPE_F16 0
+#define SAGE_DTYPE_BF16 1
+
+#define SAGE_OK 0
+#define SAGE_ERR_INVALID 1   /* bad argument (shape, alignment, dtype, null pointer) */
+#define SAGE_ERR_CUDA 2      /* a CUDA runtime / driver call failed                  */
+#define SAGE_ERR_DEVICE 3    /* the device status word reported a kernel-side error  */
+
+typedef struct sage_strided {
+  const void* ptr;
+  int64_t stride_b, stride_h, stride_s; /* in elements */
+} sage_strided_t;
+
+int sage_abi_version(void);
+const char* sage_last_error(void);
+
+/* Mean of K over the sequence, per (batch, head, channel), in the input dtype.
+ * Replaces mean_seq_gfx11 (csrc/attn_gfx11.h:48; csrc/attn_gfx11.cu:1937-1972, kernel :94-145):
+ * same fp32 summation order (256 strided partial sums, added serially), one fp32 division, one
+ * rounding.  mean_out: [B,H,D] contiguous, dtype as the input.  D must be 64 or 128. */
+int sage_mean_seq(const sage_strided_t* k, int dtype, int B, int H, int S, int D, void* mean_out, void* stream);
+
+/* Per-block INT8 quantisation of Q and K.
+ * Replaces quant_qk_int8_gfx11 (csrc/attn_gfx11.h:41-46; csrc/attn_gfx11.cu:1974-2067, kernel
+ * :147-321).  Q: groups of 32 rows, sm_scale*log2(e) folded in; K: groups of 16 rows, k_mean
+ * ([B,Hkv,D], input dtype; may be NULL) subtracted in fp32 first.
+ * Outputs: q_i8 [B,Hq,Sq,D], k_i8 [B,Hkv,Skv,D] (int8, contiguous), q_scale [B,Hq,ceil(Sq/32)],
+ * k_scale [B,Hkv,ceil(Skv/16)] (fp32).
+ * If `v` and `v16` are both non-NULL the same launch also writes v16 = fp16(v), [B,Hkv,Skv,D]
+ * contiguous: the dtype half of v_transpose_gfx11 (csrc/attn_gfx11.h:51; csrc/attn_gfx11.cu:377-381). */
+int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const void* k_mean,
+                       const sage_strided_t* v, void* v16, int dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                       int D, float sm_scale, int8_t* q_i8, float* q_scale, int8_t* k_i8, float* k_scale,
+                       void* stream);
+
+/* v16 = fp16(v), [B,H,S,D] contiguous.  The dtype half of v_transpose_gfx11
+ * (csrc/attn_gfx11.h:51); the transpose itself is an RDNA3 layout detail with no counterpart here. */
+int sage_v_to_f16(const sage_strided_t* v, int dtype, int B, int H, int S, int D, void* v16, void* stream);
+
+/* Fused INT8 attention: O = softmax2(dequant(Q_i8 K_i8^T)) V.
+ * Replaces qk_int8_sv_bf16_attn_gfx11_t (csrc/attn_gfx11.h:10-19; csrc/attn_gfx11.cu:2069-2273,
+ * kernels :409-1243).  q_i8/k_i8/scales as produced by sage_quant_qk_int8; v16 is fp16 in any
+ * strided layout; `o` has strides (o_stride_b, o_stride_h, o_stride_s) in elements and dtype
+ * `out_dtype` (SAGE_DTYPE_*).  Hq must be a multiple of Hkv (GQA: hkv = hq / (Hq/Hkv)).
+ * is_causal masks col > row (top-left aligned).
+ * s_dump (optional, may be NULL): [B,Hq,Sq,Skv] int32, receives the raw Q_i8.K_i8^T products of
+ * every KV tile the kernel visits (debug / parity aid, slow).
+ * status (optional, may be NULL): one device int that the caller zeroes; it stays 0 unless the
+ * kernel gave up on an internal wait or found its shared memory misaligned. */
+int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                             int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                             const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv, int D,
+                             int is_causal, int32_t* s_dump, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGE_B200_H_ */

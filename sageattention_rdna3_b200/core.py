@@ -1,0 +1,165 @@
+"""``sageattn`` for NVIDIA B200: the Python entry point of LuXuxue/sageattention-rdna3
+(``sageattention/core.py:40-233``) in front of hand-written sm_100a kernels.
+
+Same call, same defaults, same assertions as the reference.  What is gone: the Triton default and
+the ``SAGEATTN_BACKEND`` switch (``core.py:8,68-76``), the un-quantised "direct" kernels and their
+size thresholds (``core.py:113-163``) and the transposed V scratch (``core.py:173-180``).  Every
+call runs the INT8 path: [K mean] -> quantise Q/K (+ fp16 copy of a bf16 V) -> fused attention.
+There is no CPU or PyTorch fallback; without the compiled extension the call raises.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Dict, Optional, Tuple, Union
+
+import torch
+
+from . import _native
+
+_BACKEND = "native"          # the reference's scripts read this name (core.py:8)
+_LAYOUT_CODE = {"NHD": 0, "HND": 1}   # csrc/attn_gfx11.cu:32-33
+
+_status_words: Dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device that the attention kernel sets if it had to give up on a wait."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(idx)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = word
+    return word
+
+
+def check_status(device: Union[torch.device, int, None] = None) -> None:
+    """Synchronise and raise if a kernel on ``device`` reported an internal error since the last check."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    elif isinstance(device, int):
+        device = torch.device("cuda", device)
+    word = _status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"sageattn: the attention kernel reported device status {code} "
+                           "(1 = shared memory misaligned, 2+16*k = bounded wait k timed out)")
+
+
+def _aligned(t: torch.Tensor) -> bool:
+    return t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])
+
+
+def sageattn(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    tensor_layout: str = "HND",
+    is_causal: bool = False,
+    sm_scale: Optional[float] = None,
+    return_lse: bool = False,
+    smooth_k: bool = False,
+    **kwargs: Any,
+) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+    """INT8-QK / FP16-PV attention.  Signature and checks of ``sageattention/core.py:40-63``.
+
+    q: ``[B,Hq,Sq,D]`` ("HND") or ``[B,Sq,Hq,D]`` ("NHD"); k, v likewise with Hkv, Skv
+    (Hq a multiple of Hkv).  D in {64, 128}; fp16 / bf16, or fp32 which is computed in fp16 and
+    returned in fp32 (``core.py:78-83,200-201``).  ``smooth_k`` subtracts the per-channel mean of K
+    before quantisation (``core.py:186-190``; default False as in the native path).  Unknown keyword
+    arguments are ignored, as in the reference.  ``return_lse`` returns the reference's placeholder
+    zeros ``[B,Hq,Sq]`` (``core.py:203-211``).
+    """
+    dtype = q.dtype
+    assert q.is_cuda, "Input tensors must be on CUDA/HIP device."
+    assert dtype in [torch.float16, torch.bfloat16, torch.float32], (
+        "Input tensors must be fp16, bf16, or fp32."
+    )
+    assert q.device == k.device == v.device, "All tensors must be on the same device."
+    assert q.dtype == k.dtype == v.dtype, "All tensors must have the same dtype."
+    assert tensor_layout in _LAYOUT_CODE, f"tensor_layout must be 'HND' or 'NHD', got {tensor_layout!r}."
+    assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4, "q, k, v must be 4-D tensors."
+
+    headdim = q.size(-1)
+    assert headdim in [64, 128], f"head_dim must be 64 or 128, got {headdim}."
+    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1, (
+        "Last dim of qkv must be contiguous."
+    )
+    if sm_scale is None:
+        sm_scale = headdim ** -0.5
+
+    input_dtype = dtype
+    if dtype == torch.float32:
+        q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+        dtype = torch.float16
+
+    # core.py:91-95: the output inherits q's strides and is written with 16-byte vector stores.
+    assert q.stride(0) % 8 == 0 and q.stride(1) % 8 == 0 and q.stride(2) % 8 == 0, (
+        "native backend requires q strides that are multiples of 8 halfs "
+        "(16B aligned write-back). "
+        f"Got strides={q.stride()}. Use contiguous tensors."
+    )
+    ops = _native.load_ops()
+    layout = _LAYOUT_CODE[tensor_layout]
+    seq_dim, head_dim_idx = (2, 1) if tensor_layout == "HND" else (1, 2)
+    q_len, kv_len = q.size(seq_dim), k.size(seq_dim)
+    assert k.shape == v.shape, "k and v must have the same shape."
+    assert q.size(0) == k.size(0) and q.size(head_dim_idx) % max(k.size(head_dim_idx), 1) == 0, (
+        "batch sizes must match and num_qo_heads must be a multiple of num_kv_heads."
+    )
+    # 16-byte vector loads and TMA need aligned bases and strides; the reference leaves that to
+    # the caller for k and v, here a misaligned view is copied once.
+    if q.data_ptr() % 16 != 0:
+        q = q.clone(memory_format=torch.contiguous_format)
+    if not _aligned(k):
+        k = k.contiguous()
+    if not _aligned(v):
+        v = v.contiguous()
+
+    o = torch.empty_like(q)
+    if q_len == 0 or q.size(0) == 0 or q.size(head_dim_idx) == 0:
+        pass
+    elif kv_len == 0:
+        o.zero_()                        # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
+    else:
+        with torch.cuda.device(q.device):
+            if smooth_k:
+                k_mean = ops.mean_seq(k, layout)
+            else:
+                k_mean = torch.empty(0, device=q.device, dtype=q.dtype)
+            if dtype == torch.bfloat16:
+                # P.V runs in fp16 (csrc/attn_gfx11.cu:377-381): one launch quantises Q/K and
+                # writes the fp16 copy of V, [B,Hkv,Skv,D] contiguous.
+                q_int8, q_scale, k_int8, k_scale, v16 = ops.prep_qkv(q, k, v, k_mean, layout, sm_scale)
+                v_layout = _LAYOUT_CODE["HND"]
+            else:
+                q_int8, q_scale, k_int8, k_scale = ops.quant_qk_int8(q, k, k_mean, layout, sm_scale)
+                v16, v_layout = v, layout
+            ops.qk_int8_sv_f16_attn(q_int8, k_int8, v16, o, q_scale, k_scale, layout, v_layout,
+                                    int(is_causal), sm_scale, None, _status_word(q.device))
+        if os.environ.get("SAGEATTN_B200_CHECK_STATUS", "0") == "1":
+            check_status(q.device)
+
+    if input_dtype == torch.float32:
+        o = o.to(torch.float32)
+
+    if return_lse:
+        # LSE is not computed by the reference kernel; it returns zeros as a placeholder
+        lse = torch.zeros((q.size(0), q.size(head_dim_idx), q_len), dtype=torch.float32, device=q.device)
+        return o, lse
+    return o
+
+
+def sageattn_qk_int8_pv_fp16_cuda(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    tensor_layout: str = "HND",
+    is_causal: bool = False,
+    sm_scale: Optional[float] = None,
+    return_lse: bool = False,
+    **kwargs: Any,
+) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+    """Alias kept for callers of upstream SageAttention (``sageattention/core.py:216-233``)."""
+    return sageattn(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
+                    return_lse=return_lse, **kwargs)

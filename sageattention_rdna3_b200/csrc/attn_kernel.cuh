@@ -1,0 +1,397 @@
+// Fused INT8 attention for sm_100a: replaces attn_kernel_impl_t / attn_kernel_impl_32_t and the
+// WMMA helpers of the reference (csrc/attn_gfx11.cu:409-1243, csrc/mma_gfx11.h).
+//
+// One CTA owns one 128-row query tile of one (batch, query head) and streams the KV sequence in
+// 128-row tiles:
+//   warp 4   : TMA producer   - Q once, then K (int8) and V (fp16) tiles into a shared-memory ring
+//   warp 5   : MMA issuer     - S = Q.K^T  (tcgen05.mma kind::i8, int32 accumulator in TMEM),
+//                               O += P.V   (tcgen05.mma kind::f16, P read from TMEM, fp32 accumulator)
+//   warps 0-3: softmax        - thread t owns query row t: tcgen05.ld of S, dequantise with
+//                               q_scale[row/32]*k_scale[col/16], causal / length mask, base-2 online
+//                               softmax in fp32, P rounded to fp16 and written back into TMEM over S,
+//                               lazy rescale of O, final normalisation and store.
+// Two CTAs fit on one SM (112 KB of shared memory and 256 TMEM columns each), so the tensor pipe of
+// one overlaps the softmax of the other.
+//
+// TMEM columns: [0,128) S as int32, reused in place as P (fp16 pairs in columns [0,64));
+//               [128,128+D) O as fp32.
+// Numerics follow csrc/attn_gfx11.cu:487-502,608-689,769-786: exact int32 scores, fp32 softmax in
+// base 2 with the row sum taken before P is rounded, P in fp16, V in fp16, fp32 accumulation, one
+// rounding of acc/l to the output type.  The running maximum is only moved when it grows by more
+// than 2^8 ("lazy rescale"); acc and l use the same maximum, so acc/l is unchanged by that.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cfloat>
+#include <cstdint>
+
+#include "ptx_sm100.cuh"
+
+namespace sage {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kAttnThreads = 192;
+constexpr int kTmemCols = 256;
+constexpr int kColS = 0;
+constexpr int kColP = 0;
+constexpr int kColO = 128;
+constexpr float kMaskValue = -FLT_MAX * 0.5f;       // csrc/attn_gfx11.cu:499,628-631
+constexpr float kLazyRescaleLog2 = 8.0f;
+
+// Device status codes written to AttnParams::status (0 = ok).
+enum AttnStatus : int {
+  kStatusOk = 0,
+  kStatusSmemMisaligned = 1,
+  kStatusWaitTimeout = 2,       // + 16 * (id of the barrier the wait gave up on)
+};
+
+struct AttnParams {
+  const float* q_scale;         // [B,Hq,q_groups]
+  const float* k_scale;         // [B,Hkv,k_groups]
+  void* o;                      // caller layout; fp16 or bf16
+  long long o_stride_b, o_stride_h, o_stride_s;   // elements
+  int B, Hq, Hkv, Sq, Skv;
+  int q_groups, k_groups;
+  int n_q_tiles;
+  int out_bf16;
+  int32_t* s_dump;              // optional [B,Hq,Sq,Skv] int32 copy of Q.K^T (debug / parity)
+  int* status;                  // optional device word, stays 0 on success
+};
+
+template <int D>
+struct AttnSmem {
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kQBytes = kBlockM * D;            // int8
+  static constexpr int kKBytes = kBlockN * D;            // int8
+  static constexpr int kVBytes = kBlockN * D * 2;        // fp16
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kOffQ + kQBytes;
+  static constexpr int kOffV = kOffK + kStages * kKBytes;
+  static constexpr int kOffBar = kOffV + kStages * kVBytes;
+  // barriers: q_full, s_full, p_full, o_final, then k_full[], v_full[], kv_empty[]
+  static constexpr int kNumBars = 4 + 3 * kStages;
+  static constexpr int kOffMisc = kOffBar + 8 * kNumBars;   // tmem base (u32), abort flag (int)
+  static constexpr int kTotal = kOffMisc + 16;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(kAttnThreads, 2)
+sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  using L = AttnSmem<D>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ __align__(1024) uint8_t smem[];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Heaviest (last) query tiles first; neighbouring CTAs are heads of the same batch, so the query
+  // heads of one KV head (GQA) run together and share K/V through L2.
+  const int n_bh = p.B * p.Hq;
+  const int bh = blockIdx.x % n_bh;
+  const int qt = p.n_q_tiles - 1 - blockIdx.x / n_bh;
+  const int b = bh / p.Hq;
+  const int hq = bh % p.Hq;
+  const int hkv = hq / (p.Hq / p.Hkv);                              // csrc/attn_gfx11.cu:464
+  const int q_base = qt * kBlockM;
+  const int kv_limit = CAUSAL ? min(q_base + kBlockM, p.Skv) : p.Skv;   // csrc/attn_gfx11.cu:502
+  const int n_kv = (kv_limit + kBlockN - 1) / kBlockN;
+
+  if ((smem_u32(smem) & 1023u) != 0u) {        // swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, kStatusSmemMisaligned);
+    return;
+  }
+
+  uint8_t* s_q = smem + L::kOffQ;
+  uint8_t* s_k = smem + L::kOffK;
+  uint8_t* s_v = smem + L::kOffV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+  uint64_t* q_full = bars + 0;
+  uint64_t* s_full = bars + 1;
+  uint64_t* p_full = bars + 2;
+  uint64_t* o_final = bars + 3;
+  uint64_t* k_full = bars + 4;
+  uint64_t* v_full = bars + 4 + kStages;
+  uint64_t* kv_empty = bars + 4 + 2 * kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
+  int* fail_code = reinterpret_cast<int*>(smem + L::kOffMisc + 8);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    *fail_code = 0;
+    mbar_init(q_full, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_final, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(k_full + s, 1);
+      mbar_init(v_full + s, 1);
+      mbar_init(kv_empty + s, 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+// A failed wait records which barrier it was and leaves the role's loop.
+#define SAGE_WAIT_OR(bar_ptr, parity, bar_id, action)              \
+  if (!mbar_wait((bar_ptr), (parity), abort_flag)) {               \
+    atomicCAS(fail_code, 0, kStatusWaitTimeout + 16 * (bar_id));   \
+    action;                                                        \
+  }
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_kv > 0) {
+      mbar_arrive_expect_tx(q_full, L::kQBytes);
+      tma_load_3d(s_q, &tm_q, q_full, 0, q_base, bh);
+      const int bhkv = b * p.Hkv + hkv;
+#pragma unroll 1
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        SAGE_WAIT_OR(kv_empty + s, ph ^ 1u, 1, break);
+        mbar_arrive_expect_tx(k_full + s, L::kKBytes);
+        tma_load_3d(s_k + s * L::kKBytes, &tm_k, k_full + s, 0, j * kBlockN, bhkv);
+        mbar_arrive_expect_tx(v_full + s, L::kVBytes);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_4d(s_v + s * L::kVBytes + h * (kBlockN * 128), &tm_v, v_full + s, h * 64, j * kBlockN, hkv, b);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t kIdescQK = umma_idesc(2, 1, 1, 0, 0, kBlockM, kBlockN);   // s32 = s8 x s8
+      constexpr uint32_t kIdescPV = umma_idesc(1, 0, 0, 0, 1, kBlockM, D);         // f32 = f16 x f16, V MN-major
+      constexpr uint32_t kSwzQK = (D == 128) ? kSwizzle128B : kSwizzle64B;
+      constexpr uint32_t kSboQK = 8 * D;               // 8 rows of D bytes
+      const uint64_t desc_q = umma_smem_desc(smem_u32(s_q), 16, kSboQK, kSwzQK);
+      const uint32_t t_s = tmem_base + kColS;
+      const uint32_t t_p = tmem_base + kColP;
+      const uint32_t t_o = tmem_base + kColO;
+      bool ok = true;
+      SAGE_WAIT_OR(q_full, 0, 2, ok = false);
+#pragma unroll 1
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1;
+        SAGE_WAIT_OR(k_full + s, ph, 3, break);
+        tc_fence_after();
+        const uint64_t desc_k = umma_smem_desc(smem_u32(s_k + s * L::kKBytes), 16, kSboQK, kSwzQK);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) {             // 32 int8 of head_dim per instruction
+          mma_i8_ss(t_s, desc_q + 2 * k, desc_k + 2 * k, kIdescQK, k > 0 ? 1u : 0u);
+        }
+        tc_commit(s_full);
+        SAGE_WAIT_OR(p_full, j & 1, 4, break);
+        SAGE_WAIT_OR(v_full + s, ph, 5, break);
+        tc_fence_after();
+        // V tile: [128 kv rows][64 fp16] blocks of 16 KB, one per 64 columns of head_dim
+        const uint64_t desc_v =
+            umma_smem_desc(smem_u32(s_v + s * L::kVBytes), kBlockN * 128, 1024, kSwizzle128B);
+#pragma unroll
+        for (int k = 0; k < kBlockN / 16; ++k) {       // 16 kv rows per instruction = 2048 bytes
+          mma_f16_ts(t_o, t_p + 8 * k, desc_v + 128 * k, kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(kv_empty + s);
+      }
+      tc_commit(o_final);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue
+    const int row = q_base + threadIdx.x;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_base + kColS;
+    const uint32_t t_p = tmem_base + lane_base + kColP;
+    const uint32_t t_o = tmem_base + lane_base + kColO;
+    const int q_grp = (q_base + warp * 32) / 32;
+    const float qs = (q_grp < p.q_groups) ? __ldg(p.q_scale + static_cast<long long>(bh) * p.q_groups + q_grp) : 0.0f;
+    const float* ks_base = p.k_scale + static_cast<long long>(b * p.Hkv + hkv) * p.k_groups;
+
+    float m_used = kMaskValue;
+    float l = 0.0f;
+    bool ok = true;
+
+#pragma unroll 1
+    for (int j = 0; j < n_kv; ++j) {
+      const int kv_base = j * kBlockN;
+      SAGE_WAIT_OR(s_full, j & 1, 6, { ok = false; break; });
+      tc_fence_after();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + 32 * c, sr[c]);
+      tc_wait_ld();
+
+      if (p.s_dump != nullptr && row < p.Sq) {
+        int32_t* dst = p.s_dump + (static_cast<long long>(bh) * p.Sq + row) * p.Skv + kv_base;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kv_base + 32 * c + i < p.Skv) dst[32 * c + i] = static_cast<int32_t>(sr[c][i]);
+      }
+
+      float cg[8];                                      // q_scale * k_scale per 16 columns (:621)
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int kg = kv_base / 16 + g;
+        cg[g] = (kg < p.k_groups) ? __fmul_rn(qs, __ldg(ks_base + kg)) : 0.0f;
+      }
+
+      const bool masked_tile = (CAUSAL && kv_base + kBlockN - 1 > q_base) || (kv_base + kBlockN > p.Skv);
+      // columns below this bound are visible to this row (causal: col <= row; length: col < Skv)
+      const int col_end = masked_tile ? min(p.Skv, CAUSAL ? row + 1 : p.Skv) - kv_base : kBlockN;
+
+      float m_tile = kMaskValue;
+      if (!masked_tile) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {                   // scales are >= 0: max commutes with the scaling
+          int mx = static_cast<int>(sr[g >> 1][(g & 1) * 16]);
+#pragma unroll
+          for (int i = 1; i < 16; ++i) mx = max(mx, static_cast<int>(sr[g >> 1][(g & 1) * 16 + i]));
+          m_tile = fmaxf(m_tile, __int2float_rn(mx) * cg[g]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float sv = __int2float_rn(static_cast<int>(sr[c][i])) * cg[(32 * c + i) >> 4];
+            if (32 * c + i < col_end) m_tile = fmaxf(m_tile, sv);
+          }
+      }
+
+      // lazy rescale: move the running maximum only when it grew by more than 2^8
+      if (j == 0) {
+        m_used = m_tile;
+      } else {
+        const bool need = m_tile > m_used + kLazyRescaleLog2;
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = need ? fast_exp2(m_used - m_tile) : 1.0f;   // (:667)
+          if (need) m_used = m_tile;
+          l *= alpha;
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld32(t_o + 32 * c, orr);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+            tmem_st32(t_o + 32 * c, orr);
+          }
+        }
+      }
+
+      // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs back into TMEM
+      float l_add0 = 0.0f, l_add1 = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int e = 32 * c + 2 * i;
+          const float cs = cg[e >> 4];
+          float p0 = fast_exp2(fmaf(__int2float_rn(static_cast<int>(sr[c][2 * i])), cs, -m_used));
+          float p1 = fast_exp2(fmaf(__int2float_rn(static_cast<int>(sr[c][2 * i + 1])), cs, -m_used));
+          if (masked_tile) {
+            if (e >= col_end) p0 = 0.0f;
+            if (e + 1 >= col_end) p1 = 0.0f;
+          }
+          l_add0 += p0;
+          l_add1 += p1;
+          pk[i] = pack_half2(p0, p1);
+        }
+        tmem_st16(t_p + 16 * c, pk);
+      }
+      l += l_add0 + l_add1;
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+
+    // ---- epilogue: o = acc * (1/l), one rounding to the output type (:769-786)
+    if (ok && n_kv > 0) {
+      SAGE_WAIT_OR(o_final, 0, 7, ok = false);
+      tc_fence_after();
+    }
+    if (ok) {
+      const float inv_l = (l > 0.0f) ? (1.0f / l) : 0.0f;
+      uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +
+                       2 * (b * p.o_stride_b + hq * p.o_stride_h + static_cast<long long>(row) * p.o_stride_s);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t orr[32];
+        if (n_kv > 0) {
+          tmem_ld32(t_o + 32 * c, orr);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) orr[i] = 0u;
+        }
+        if (row < p.Sq) {
+          uint32_t out[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float a = __uint_as_float(orr[2 * i]) * inv_l;
+            const float bb = __uint_as_float(orr[2 * i + 1]) * inv_l;
+            out[i] = p.out_bf16 ? pack_bf162(a, bb) : pack_half2(a, bb);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(o_row + 64 * c);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+        }
+      }
+    }
+  }
+#undef SAGE_WAIT_OR
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up.  Let copies and MMAs that are still in flight land before the shared memory
+    // and TMEM of this CTA are handed back, then report.
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, *fail_code ? *fail_code : kStatusWaitTimeout);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace sage

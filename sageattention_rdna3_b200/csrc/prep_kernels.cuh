@@ -1,0 +1,249 @@
+// Preparation kernels of the INT8 attention path (HBM-bound byte work):
+//   * sage_kmean_kernel : per-(b,h,d) mean of K over the sequence (only for smooth_k);
+//   * sage_prep_kernel  : per-block INT8 quantisation of Q (32-row groups, sm_scale*log2e folded
+//                         in) and of K (16-row groups, optional mean subtraction) with fp32 scales,
+//                         plus, in the same launch, the bf16 -> fp16 copy of V that P.V consumes.
+// They replace mean_hnd_kernel, quant_qk_int8_hnd_kernel and the dtype half of v_transpose_kernel
+// of the reference (csrc/attn_gfx11.cu:94-145, :147-321, :326-407).
+//
+// Bit-exactness.  The quantisation arithmetic is written with __fmul_rn/__fadd_rn/__fdiv_rn so
+// that nvcc cannot contract a multiply and an add into an FMA; the results are the ones separate
+// IEEE fp32 operations give.  The group maximum is taken on the un-scaled magnitudes and scaled
+// once: fp32 rounding is monotone, so max_i fl(|x_i|*s) == fl(max_i|x_i| * s).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <type_traits>
+
+namespace sage {
+
+struct StridedView {        // one of q / k / v in the caller's layout, strides in elements
+  const void* ptr;
+  long long stride_b, stride_h, stride_s;
+};
+
+struct PrepParams {
+  StridedView q, k, v;
+  int8_t* q_i8;             // [B,Hq,Sq,D]
+  int8_t* k_i8;             // [B,Hkv,Skv,D]
+  float* q_scale;           // [B,Hq,ceil(Sq/32)]
+  float* k_scale;           // [B,Hkv,ceil(Skv/16)]
+  const void* k_mean;       // [B,Hkv,D] in the input dtype, or nullptr
+  __half* v16;              // [B,Hkv,Skv,D] fp16 copy of V, or nullptr (no conversion)
+  int B, Hq, Hkv, Sq, Skv;
+  int q_groups, k_groups;   // ceil(Sq/32), ceil(Skv/16)
+  float sm_scale_log2e;
+  int q_blocks, k_blocks;   // CTAs spent on Q groups, on K groups; the rest convert V
+};
+
+constexpr int kPrepThreads = 256;
+constexpr int kPrepWarps = kPrepThreads / 32;
+constexpr int kQGroupRows = 32;   // csrc/attn_gfx11.cu:46
+constexpr int kKGroupRows = 16;   // csrc/attn_gfx11.cu:47
+
+template <typename T> __device__ __forceinline__ float elem_to_float(T v);
+template <> __device__ __forceinline__ float elem_to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float elem_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+// csrc/attn_gfx11.cu:85-92: add +-0.5, convert toward zero, clamp to [-128, 127].
+__device__ __forceinline__ int quantise_one(float y) {
+  y = __fadd_rn(y, (y >= 0.0f) ? 0.5f : -0.5f);
+  int r = __float2int_rz(y);
+  r = r > 127 ? 127 : r;
+  r = r < -128 ? -128 : r;
+  return r;
+}
+
+// One warp quantises one group of ROWS consecutive rows (all D columns) of one (b,h).
+// A row is D/8 lanes x 16 bytes, so a warp reads 32*8/D rows per 512-byte load.
+template <typename T, int D, int ROWS>
+__device__ __forceinline__ void quantise_group(const T* __restrict__ in_bh, long long stride_s, int row0, int S,
+                                               int8_t* __restrict__ out_bh, float* __restrict__ scale_out,
+                                               float s_mul, const T* __restrict__ mean_bh, int lane) {
+  constexpr int kLanesPerRow = D / 8;
+  constexpr int kRowsPerPass = 32 / kLanesPerRow;
+  constexpr int kPasses = ROWS / kRowsPerPass;
+  const int sub = lane / kLanesPerRow;
+  const int col = (lane % kLanesPerRow) * 8;
+
+  float mean8[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mean8[i] = 0.0f;
+  if (mean_bh != nullptr) {
+    const uint4 mraw = *reinterpret_cast<const uint4*>(mean_bh + col);
+    const T* mv = reinterpret_cast<const T*>(&mraw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mean8[i] = elem_to_float<T>(mv[i]);
+  }
+
+  uint4 raw[kPasses];
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const int row = row0 + p * kRowsPerPass + sub;
+    raw[p] = make_uint4(0u, 0u, 0u, 0u);
+    if (row < S) raw[p] = __ldg(reinterpret_cast<const uint4*>(in_bh + static_cast<long long>(row) * stride_s + col));
+  }
+
+  // pass 1 (csrc/attn_gfx11.cu:189-237): group abs-max of (x - mean)
+  float vmax = 0.0f;
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const int row = row0 + p * kRowsPerPass + sub;
+    if (row < S) {
+      const T* xv = reinterpret_cast<const T*>(&raw[p]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float v = __fsub_rn(elem_to_float<T>(xv[i]), mean8[i]);
+        vmax = fmaxf(vmax, fabsf(v));
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+
+  const float amax = fmaxf(1e-7f, __fmul_rn(vmax, fabsf(s_mul)));      // :192,224
+  if (lane == 0) *scale_out = __fdiv_rn(amax, 127.0f);                 // :244-245
+  const float iscale = __fmul_rn(__fdiv_rn(127.0f, amax), s_mul);      // :252,296
+
+  // pass 2 (csrc/attn_gfx11.cu:250-318): quantise from the registers, 8 bytes per lane and row
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const int row = row0 + p * kRowsPerPass + sub;
+    if (row < S) {
+      const T* xv = reinterpret_cast<const T*>(&raw[p]);
+      uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float v = __fsub_rn(elem_to_float<T>(xv[i]), mean8[i]);
+        const int qv = quantise_one(__fmul_rn(v, iscale));
+        packed[i >> 2] |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * (i & 3));
+      }
+      *reinterpret_cast<uint2*>(out_bh + static_cast<long long>(row) * D + col) = make_uint2(packed[0], packed[1]);
+    }
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPrepThreads) sage_prep_kernel(const PrepParams p) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int blk = blockIdx.x;
+
+  if (blk < p.q_blocks) {                                   // ---- Q groups, one per warp
+    const long long g = static_cast<long long>(blk) * kPrepWarps + warp;
+    const long long total = static_cast<long long>(p.B) * p.Hq * p.q_groups;
+    if (g >= total) return;
+    const int grp = static_cast<int>(g % p.q_groups);
+    const int bh = static_cast<int>(g / p.q_groups);
+    const int b = bh / p.Hq, h = bh % p.Hq;
+    const T* in_bh = reinterpret_cast<const T*>(p.q.ptr) + b * p.q.stride_b + h * p.q.stride_h;
+    quantise_group<T, D, kQGroupRows>(in_bh, p.q.stride_s, grp * kQGroupRows, p.Sq,
+                                      p.q_i8 + static_cast<long long>(bh) * p.Sq * D, p.q_scale + g,
+                                      p.sm_scale_log2e, nullptr, lane);
+    return;
+  }
+  blk -= p.q_blocks;
+  if (blk < p.k_blocks) {                                   // ---- K groups, one per warp
+    const long long g = static_cast<long long>(blk) * kPrepWarps + warp;
+    const long long total = static_cast<long long>(p.B) * p.Hkv * p.k_groups;
+    if (g >= total) return;
+    const int grp = static_cast<int>(g % p.k_groups);
+    const int bh = static_cast<int>(g / p.k_groups);
+    const int b = bh / p.Hkv, h = bh % p.Hkv;
+    const T* in_bh = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h;
+    const T* mean_bh =
+        p.k_mean ? reinterpret_cast<const T*>(p.k_mean) + static_cast<long long>(bh) * D : nullptr;
+    quantise_group<T, D, kKGroupRows>(in_bh, p.k.stride_s, grp * kKGroupRows, p.Skv,
+                                      p.k_i8 + static_cast<long long>(bh) * p.Skv * D, p.k_scale + g, 1.0f,
+                                      mean_bh, lane);
+    return;
+  }
+  blk -= p.k_blocks;
+  // ---- V: 16-bit copy to fp16 [B,Hkv,Skv,D] (csrc/attn_gfx11.cu:377-381: __float2half_rn).
+  // Each thread converts four 16-byte vectors, 4096 bytes apart, so a warp moves 512 B per load.
+  if (p.v16 == nullptr) return;
+  constexpr int kVecPerRow = D / 8;
+  const long long n_vec = static_cast<long long>(p.B) * p.Hkv * p.Skv * kVecPerRow;
+  const long long base = static_cast<long long>(blk) * (kPrepThreads * 4) + threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long vec = base + static_cast<long long>(i) * kPrepThreads;
+    if (vec < n_vec) {
+      const int c = static_cast<int>(vec % kVecPerRow) * 8;
+      const long long row = vec / kVecPerRow;
+      const int s = static_cast<int>(row % p.Skv);
+      const int bh = static_cast<int>(row / p.Skv);
+      const int b = bh / p.Hkv, h = bh % p.Hkv;
+      const T* src = reinterpret_cast<const T*>(p.v.ptr) + b * p.v.stride_b + h * p.v.stride_h +
+                     static_cast<long long>(s) * p.v.stride_s + c;
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+      const T* xv = reinterpret_cast<const T*>(&raw);
+      uint4 out;
+      uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 h2 = __floats2half2_rn(elem_to_float<T>(xv[2 * j]), elem_to_float<T>(xv[2 * j + 1]));
+        o32[j] = *reinterpret_cast<const uint32_t*>(&h2);
+      }
+      *reinterpret_cast<uint4*>(p.v16 + vec * 8) = out;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// K mean over the sequence, in the reference's summation order (csrc/attn_gfx11.cu:94-145):
+// 256 partial sums (thread t adds rows t, t+256, ... in fp32), then the 256 partials are added
+// serially from 0 to 255, then one fp32 division by float(S) and one rounding to the input type.
+// One CTA = one (b, h, 16-column slab); a thread reads 32 contiguous bytes of every row it owns.
+struct MeanParams {
+  StridedView k;
+  void* mean_out;   // [B,H,D] in the input dtype
+  int B, H, S, D;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) sage_kmean_kernel(const MeanParams p) {
+  constexpr int kCols = 16;
+  __shared__ float partial[kCols][257];
+  const int tid = threadIdx.x;
+  const int d0 = blockIdx.x * kCols;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const T* base = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h + d0;
+
+  float acc[kCols];
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) acc[c] = 0.0f;
+#pragma unroll 4
+  for (int s = tid; s < p.S; s += 256) {
+    const uint4* src = reinterpret_cast<const uint4*>(base + static_cast<long long>(s) * p.k.stride_s);
+    const uint4 r0 = __ldg(src), r1 = __ldg(src + 1);
+    const T* v0 = reinterpret_cast<const T*>(&r0);
+    const T* v1 = reinterpret_cast<const T*>(&r1);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      acc[c] = __fadd_rn(acc[c], elem_to_float<T>(v0[c]));
+      acc[8 + c] = __fadd_rn(acc[8 + c], elem_to_float<T>(v1[c]));
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) partial[c][tid] = acc[c];
+  __syncthreads();
+  if (tid < kCols) {
+    float sum = 0.0f;
+#pragma unroll 8
+    for (int i = 0; i < 256; ++i) sum = __fadd_rn(sum, partial[tid][i]);
+    const float value = __fdiv_rn(sum, static_cast<float>(p.S));
+    T* out = reinterpret_cast<T*>(p.mean_out) + (static_cast<long long>(b) * p.H + h) * p.D + d0 + tid;
+    if constexpr (std::is_same<T, __half>::value) {
+      *out = __float2half_rn(value);
+    } else {
+      *out = __float2bfloat16_rn(value);
+    }
+  }
+}
+
+}  // namespace sage

@@ -1,0 +1,287 @@
+// Host side of the C ABI declared in include/sage_b200.h: argument checks, TMA tensor maps,
+// kernel selection and launches.  No torch types, no allocation, no synchronisation.
+#include "../../include/sage_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "attn_kernel.cuh"
+#include "prep_kernels.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define SAGE_REQUIRE(cond, ...) \
+  do {                          \
+    if (!(cond)) return fail(SAGE_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+#define SAGE_CUDA(expr)                                                                        \
+  do {                                                                                         \
+    cudaError_t e_ = (expr);                                                                   \
+    if (e_ != cudaSuccess) return fail(SAGE_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool strides_ok(const sage_strided_t* t) {
+  return t->stride_b % 8 == 0 && t->stride_h % 8 == 0 && t->stride_s % 8 == 0;
+}
+sage::StridedView view_of(const sage_strided_t* t) {
+  sage::StridedView v;
+  v.ptr = t->ptr;
+  v.stride_b = t->stride_b;
+  v.stride_h = t->stride_h;
+  v.stride_s = t->stride_s;
+  return v;
+}
+
+// cuTensorMapEncodeTiled is taken from the driver at run time, so the library links against the
+// CUDA runtime only.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims,
+               const cuuint64_t* strides_bytes, const cuuint32_t* box, CUtensorMapSwizzle swz, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(SAGE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims, strides_bytes, box, ones,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SAGE_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  return SAGE_OK;
+}
+
+template <typename T, int D>
+int launch_prep(const sage::PrepParams& p, int v_blocks, cudaStream_t stream) {
+  const int grid = p.q_blocks + p.k_blocks + v_blocks;
+  if (grid == 0) return SAGE_OK;
+  sage::sage_prep_kernel<T, D><<<grid, sage::kPrepThreads, 0, stream>>>(p);
+  SAGE_CUDA(cudaGetLastError());
+  return SAGE_OK;
+}
+
+int dispatch_prep(int dtype, int D, const sage::PrepParams& p, int v_blocks, cudaStream_t stream) {
+  if (dtype == SAGE_DTYPE_F16) {
+    return D == 64 ? launch_prep<__half, 64>(p, v_blocks, stream) : launch_prep<__half, 128>(p, v_blocks, stream);
+  }
+  return D == 64 ? launch_prep<__nv_bfloat16, 64>(p, v_blocks, stream)
+                 : launch_prep<__nv_bfloat16, 128>(p, v_blocks, stream);
+}
+
+int v_block_count(long long B, long long H, long long S, int D) {
+  const long long n_vec = B * H * S * (D / 8);
+  return static_cast<int>((n_vec + sage::kPrepThreads * 4 - 1) / (sage::kPrepThreads * 4));
+}
+
+template <int D, bool CAUSAL>
+int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const sage::AttnParams& p,
+                cudaStream_t stream) {
+  auto kern = sage::sage_attn_kernel<D, CAUSAL>;
+  constexpr int kSmem = sage::AttnSmem<D>::kTotal;
+  static bool configured[64] = {};
+  int dev = 0;
+  SAGE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    SAGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const long long grid = static_cast<long long>(p.n_q_tiles) * p.B * p.Hq;
+  if (grid > 0x7fffffffLL) return fail(SAGE_ERR_INVALID, "too many query tiles for one launch (%lld)", grid);
+  kern<<<static_cast<unsigned>(grid), sage::kAttnThreads, kSmem, stream>>>(tq, tk, tv, p);
+  SAGE_CUDA(cudaGetLastError());
+  return SAGE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sage_abi_version(void) { return SAGE_ABI_VERSION; }
+const char* sage_last_error(void) { return g_err; }
+
+int sage_mean_seq(const sage_strided_t* k, int dtype, int B, int H, int S, int D, void* mean_out, void* stream) {
+  SAGE_REQUIRE(k && k->ptr && mean_out, "sage_mean_seq: null pointer");
+  SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_mean_seq: dtype must be f16 or bf16");
+  SAGE_REQUIRE(D == 64 || D == 128, "sage_mean_seq: head_dim must be 64 or 128, got %d", D);
+  SAGE_REQUIRE(B > 0 && H > 0 && S > 0, "sage_mean_seq: empty tensor (B=%d H=%d S=%d)", B, H, S);
+  SAGE_REQUIRE(H <= 65535 && B <= 65535, "sage_mean_seq: B and H must be <= 65535");
+  SAGE_REQUIRE(aligned16(k->ptr) && strides_ok(k), "sage_mean_seq: k needs a 16-byte aligned base and strides % 8 == 0");
+  sage::MeanParams p;
+  p.k = view_of(k);
+  p.mean_out = mean_out;
+  p.B = B; p.H = H; p.S = S; p.D = D;
+  dim3 grid(D / 16, H, B);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == SAGE_DTYPE_F16) sage::sage_kmean_kernel<__half><<<grid, 256, 0, st>>>(p);
+  else sage::sage_kmean_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  SAGE_CUDA(cudaGetLastError());
+  return SAGE_OK;
+}
+
+int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const void* k_mean,
+                       const sage_strided_t* v, void* v16, int dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                       int D, float sm_scale, int8_t* q_i8, float* q_scale, int8_t* k_i8, float* k_scale,
+                       void* stream) {
+  SAGE_REQUIRE(q && k && q->ptr && k->ptr, "sage_quant_qk_int8: null input");
+  SAGE_REQUIRE(q_i8 && q_scale && k_i8 && k_scale, "sage_quant_qk_int8: null output");
+  SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_quant_qk_int8: dtype must be f16 or bf16");
+  SAGE_REQUIRE(D == 64 || D == 128, "sage_quant_qk_int8: head_dim must be 64 or 128, got %d", D);
+  SAGE_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Sq >= 0 && Skv >= 0, "sage_quant_qk_int8: bad sizes");
+  SAGE_REQUIRE(aligned16(q->ptr) && strides_ok(q), "sage_quant_qk_int8: q needs a 16-byte aligned base and strides % 8 == 0");
+  SAGE_REQUIRE(aligned16(k->ptr) && strides_ok(k), "sage_quant_qk_int8: k needs a 16-byte aligned base and strides % 8 == 0");
+  SAGE_REQUIRE(aligned16(q_i8) && aligned16(k_i8), "sage_quant_qk_int8: int8 outputs must be 16-byte aligned");
+  SAGE_REQUIRE(k_mean == nullptr || aligned16(k_mean), "sage_quant_qk_int8: k_mean must be 16-byte aligned");
+  const bool do_v = (v != nullptr && v16 != nullptr);
+  if (do_v) {
+    SAGE_REQUIRE(v->ptr && aligned16(v->ptr) && strides_ok(v) && aligned16(v16),
+                 "sage_quant_qk_int8: v / v16 need 16-byte aligned bases and strides % 8 == 0");
+  }
+  sage::PrepParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = view_of(q);
+  p.k = view_of(k);
+  if (do_v) p.v = view_of(v);
+  p.q_i8 = q_i8; p.k_i8 = k_i8; p.q_scale = q_scale; p.k_scale = k_scale;
+  p.k_mean = k_mean;
+  p.v16 = do_v ? static_cast<__half*>(v16) : nullptr;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv;
+  p.q_groups = (Sq + sage::kQGroupRows - 1) / sage::kQGroupRows;
+  p.k_groups = (Skv + sage::kKGroupRows - 1) / sage::kKGroupRows;
+  // csrc/attn_gfx11.cu:34,1995: float(sm_scale) * 1.4426950408889634f, one fp32 multiply
+  volatile float s = sm_scale;
+  volatile float l2e = 1.4426950408889634f;
+  p.sm_scale_log2e = s * l2e;
+  const long long qg = static_cast<long long>(B) * Hq * p.q_groups;
+  const long long kg = static_cast<long long>(B) * Hkv * p.k_groups;
+  p.q_blocks = static_cast<int>((qg + sage::kPrepWarps - 1) / sage::kPrepWarps);
+  p.k_blocks = static_cast<int>((kg + sage::kPrepWarps - 1) / sage::kPrepWarps);
+  const int v_blocks = do_v ? v_block_count(B, Hkv, Skv, D) : 0;
+  return dispatch_prep(dtype, D, p, v_blocks, static_cast<cudaStream_t>(stream));
+}
+
+int sage_v_to_f16(const sage_strided_t* v, int dtype, int B, int H, int S, int D, void* v16, void* stream) {
+  SAGE_REQUIRE(v && v->ptr && v16, "sage_v_to_f16: null pointer");
+  SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_v_to_f16: dtype must be f16 or bf16");
+  SAGE_REQUIRE(D == 64 || D == 128, "sage_v_to_f16: head_dim must be 64 or 128, got %d", D);
+  SAGE_REQUIRE(B > 0 && H > 0 && S >= 0, "sage_v_to_f16: bad sizes");
+  SAGE_REQUIRE(aligned16(v->ptr) && strides_ok(v) && aligned16(v16),
+               "sage_v_to_f16: v / v16 need 16-byte aligned bases and strides % 8 == 0");
+  sage::PrepParams p;
+  memset(&p, 0, sizeof(p));
+  p.v = view_of(v);
+  p.v16 = static_cast<__half*>(v16);
+  p.B = B; p.Hq = H; p.Hkv = H; p.Sq = 0; p.Skv = S;
+  return dispatch_prep(dtype, D, p, v_block_count(B, H, S, D), static_cast<cudaStream_t>(stream));
+}
+
+int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                             int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                             const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv, int D,
+                             int is_causal, int32_t* s_dump, int* status, void* stream) {
+  SAGE_REQUIRE(q_i8 && v16 && o && q_scale, "sage_qk_int8_sv_f16_attn: null pointer");
+  SAGE_REQUIRE(Skv == 0 || (k_i8 && v16->ptr && k_scale), "sage_qk_int8_sv_f16_attn: null pointer");
+  SAGE_REQUIRE(out_dtype == SAGE_DTYPE_F16 || out_dtype == SAGE_DTYPE_BF16,
+               "sage_qk_int8_sv_f16_attn: out_dtype must be f16 or bf16");
+  SAGE_REQUIRE(D == 64 || D == 128, "sage_qk_int8_sv_f16_attn: head_dim must be 64 or 128, got %d", D);
+  SAGE_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Sq >= 0 && Skv >= 0, "sage_qk_int8_sv_f16_attn: bad sizes");
+  SAGE_REQUIRE(Hq % Hkv == 0, "sage_qk_int8_sv_f16_attn: Hq (%d) must be a multiple of Hkv (%d)", Hq, Hkv);
+  SAGE_REQUIRE(aligned16(q_i8) && aligned16(k_i8), "sage_qk_int8_sv_f16_attn: int8 inputs must be 16-byte aligned");
+  SAGE_REQUIRE(aligned16(v16->ptr) && strides_ok(v16),
+               "sage_qk_int8_sv_f16_attn: v needs a 16-byte aligned base and strides % 8 == 0");
+  SAGE_REQUIRE(aligned16(o) && o_stride_b % 8 == 0 && o_stride_h % 8 == 0 && o_stride_s % 8 == 0,
+               "sage_qk_int8_sv_f16_attn: o needs a 16-byte aligned base and strides % 8 == 0");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (Sq == 0) return SAGE_OK;
+
+  sage::AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.q_scale = q_scale; p.k_scale = k_scale;
+  p.o = o; p.o_stride_b = o_stride_b; p.o_stride_h = o_stride_h; p.o_stride_s = o_stride_s;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv;
+  p.q_groups = (Sq + sage::kQGroupRows - 1) / sage::kQGroupRows;
+  p.k_groups = (Skv + sage::kKGroupRows - 1) / sage::kKGroupRows;
+  p.n_q_tiles = (Sq + sage::kBlockM - 1) / sage::kBlockM;
+  p.out_bf16 = (out_dtype == SAGE_DTYPE_BF16);
+  p.s_dump = s_dump;
+  p.status = status;
+
+  // With no keys every row has l == 0 and the output is 0 (csrc/attn_gfx11.cu:771).  The kernel
+  // handles that without touching K or V, but a tensor map cannot have a zero extent: describe one
+  // dummy row instead (it is never loaded).
+  const int skv_map = Skv > 0 ? Skv : 1;
+  const void* k_base = Skv > 0 ? static_cast<const void*>(k_i8) : static_cast<const void*>(q_i8);
+  const void* v_base = Skv > 0 ? v16->ptr : static_cast<const void*>(q_i8);
+
+  CUtensorMap tq, tk, tv;
+  const CUtensorMapSwizzle swz_qk = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Sq, (cuuint64_t)B * Hq};
+    cuuint64_t strides[2] = {(cuuint64_t)D, (cuuint64_t)Sq * D};
+    cuuint32_t box[3] = {(cuuint32_t)D, (cuuint32_t)sage::kBlockM, 1};
+    int rc = encode_map(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, q_i8, dims, strides, box, swz_qk, "q_i8");
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)skv_map, (cuuint64_t)B * Hkv};
+    cuuint64_t strides[2] = {(cuuint64_t)D, (cuuint64_t)skv_map * D};
+    cuuint32_t box[3] = {(cuuint32_t)D, (cuuint32_t)sage::kBlockN, 1};
+    int rc = encode_map(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, k_base, dims, strides, box, swz_qk, "k_i8");
+    if (rc) return rc;
+  }
+  {
+    // A dimension of extent 1 may carry any stride in the caller's tensor; give it the span of
+    // the others so that the map stays well formed.
+    cuuint64_t ss = (cuuint64_t)v16->stride_s * 2, sh = (cuuint64_t)v16->stride_h * 2, sb = (cuuint64_t)v16->stride_b * 2;
+    cuuint64_t span = (cuuint64_t)D * 2;
+    if (skv_map > 1 && ss * skv_map > span) span = ss * skv_map;
+    if (Hkv > 1 && sh * Hkv > span) span = sh * Hkv;
+    if (B > 1 && sb * B > span) span = sb * B;
+    span = (span + 15) & ~(cuuint64_t)15;
+    if (skv_map == 1) ss = span;
+    if (Hkv == 1) sh = span;
+    if (B == 1) sb = span;
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)skv_map, (cuuint64_t)Hkv, (cuuint64_t)B};
+    cuuint64_t strides[3] = {ss, sh, sb};
+    cuuint32_t box[4] = {64, (cuuint32_t)sage::kBlockN, 1, 1};
+    int rc = encode_map(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, v_base, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B, "v16");
+    if (rc) return rc;
+  }
+
+  if (D == 128) {
+    return is_causal ? launch_attn<128, true>(tq, tk, tv, p, st) : launch_attn<128, false>(tq, tk, tv, p, st);
+  }
+  return is_causal ? launch_attn<64, true>(tq, tk, tv, p, st) : launch_attn<64, false>(tq, tk, tv, p, st);
+}
+
+}  // extern "C"
