@@ -70,9 +70,10 @@ struct AttnSmem {
   static constexpr int kOffK = kOffQ + kQBytes;
   static constexpr int kOffV = kOffK + kStages * kKBytes;
   static constexpr int kOffBar = kOffV + kStages * kVBytes;
-  // barriers: q_full, s_full, p_full, o_final, then k_full[], v_full[], kv_empty[]
-  static constexpr int kNumBars = 4 + 3 * kStages;
-  static constexpr int kOffMisc = kOffBar + 8 * kNumBars;   // tmem base (u32), abort flag (int)
+  // barriers: q_full, o_final, s_full[2], p_full[2], pv_done[2], then per stage
+  // k_full[], v_full[], k_empty[], v_empty[]
+  static constexpr int kNumBars = 8 + 4 * kStages;
+  static constexpr int kOffMisc = kOffBar + 8 * kNumBars;   // tmem base (u32), abort flag, fail code
   static constexpr int kTotal = kOffMisc + 16;
 };
 
@@ -81,15 +82,39 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  const __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));   // first source -> upper half
+  return r;
 }
 __device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
-  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
 }
+// Packed fp32 pairs (sm_100): two fused multiply-adds / adds per instruction.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+constexpr int kHalfN = kBlockN / 2;      // the softmax works on 64-column halves of a KV tile
 
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(kAttnThreads, 2)
@@ -124,12 +149,14 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint8_t* s_v = smem + L::kOffV;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* q_full = bars + 0;
-  uint64_t* s_full = bars + 1;
-  uint64_t* p_full = bars + 2;
-  uint64_t* o_final = bars + 3;
-  uint64_t* k_full = bars + 4;
-  uint64_t* v_full = bars + 4 + kStages;
-  uint64_t* kv_empty = bars + 4 + 2 * kStages;
+  uint64_t* o_final = bars + 1;
+  uint64_t* s_full = bars + 2;      // [2] one per half: S_h holds Q.K_h^T
+  uint64_t* p_full = bars + 4;      // [2] P_h written (and O rescaled) by all 128 softmax threads
+  uint64_t* pv_done = bars + 6;     // [2] O += P_h.V_h has completed
+  uint64_t* k_full = bars + 8;
+  uint64_t* v_full = bars + 8 + kStages;
+  uint64_t* k_empty = bars + 8 + 2 * kStages;
+  uint64_t* v_empty = bars + 8 + 3 * kStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 4);
   int* fail_code = reinterpret_cast<int*>(smem + L::kOffMisc + 8);
@@ -138,13 +165,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     *abort_flag = 0;
     *fail_code = 0;
     mbar_init(q_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
     mbar_init(o_final, 1);
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(s_full + h, 1);
+      mbar_init(p_full + h, 128);
+      mbar_init(pv_done + h, 1);
+    }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(k_full + s, 1);
       mbar_init(v_full + s, 1);
-      mbar_init(kv_empty + s, 1);
+      mbar_init(k_empty + s, 1);
+      mbar_init(v_empty + s, 1);
     }
     fence_mbar_init();
   }
@@ -171,17 +202,25 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
+    // Order of issue: Q, K(0), then for every tile K(j+1) before V(j): K is needed first.
     if (lane == 0 && n_kv > 0) {
+      const int bhkv = b * p.Hkv + hkv;
       mbar_arrive_expect_tx(q_full, L::kQBytes);
       tma_load_3d(s_q, &tm_q, q_full, 0, q_base, bh);
-      const int bhkv = b * p.Hkv + hkv;
+      mbar_arrive_expect_tx(k_full, L::kKBytes);
+      tma_load_3d(s_k, &tm_k, k_full, 0, 0, bhkv);
 #pragma unroll 1
       for (int j = 0; j < n_kv; ++j) {
+        if (j + 1 < n_kv) {
+          const int s1 = (j + 1) % kStages;
+          const uint32_t ph1 = ((j + 1) / kStages) & 1;
+          SAGE_WAIT_OR(k_empty + s1, ph1 ^ 1u, 1, break);
+          mbar_arrive_expect_tx(k_full + s1, L::kKBytes);
+          tma_load_3d(s_k + s1 * L::kKBytes, &tm_k, k_full + s1, 0, (j + 1) * kBlockN, bhkv);
+        }
         const int s = j % kStages;
         const uint32_t ph = (j / kStages) & 1;
-        SAGE_WAIT_OR(kv_empty + s, ph ^ 1u, 1, break);
-        mbar_arrive_expect_tx(k_full + s, L::kKBytes);
-        tma_load_3d(s_k + s * L::kKBytes, &tm_k, k_full + s, 0, j * kBlockN, bhkv);
+        SAGE_WAIT_OR(v_empty + s, ph ^ 1u, 2, break);
         mbar_arrive_expect_tx(v_full + s, L::kVBytes);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
@@ -192,40 +231,65 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncwarp();
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
+    // Program order of the tensor pipe: QK(0,0) QK(0,1) | PV(0,0) QK(1,0) PV(0,1) QK(1,1) | ...
+    // so the scores of the next half are ready while the softmax warps work on the current one.
     if (lane == 0 && n_kv > 0) {
-      constexpr uint32_t kIdescQK = umma_idesc(2, 1, 1, 0, 0, kBlockM, kBlockN);   // s32 = s8 x s8
-      constexpr uint32_t kIdescPV = umma_idesc(1, 0, 0, 0, 1, kBlockM, D);         // f32 = f16 x f16, V MN-major
+      constexpr uint32_t kIdescQK = umma_idesc(2, 1, 1, 0, 0, kBlockM, kHalfN);   // s32 = s8 x s8
+      constexpr uint32_t kIdescPV = umma_idesc(1, 0, 0, 0, 1, kBlockM, D);        // f32 = f16 x f16, V MN-major
       constexpr uint32_t kSwzQK = (D == 128) ? kSwizzle128B : kSwizzle64B;
       constexpr uint32_t kSboQK = 8 * D;               // 8 rows of D bytes
+      constexpr uint32_t kHalfKBytes = kHalfN * D;     // 64 K rows
       const uint64_t desc_q = umma_smem_desc(smem_u32(s_q), 16, kSboQK, kSwzQK);
-      const uint32_t t_s = tmem_base + kColS;
-      const uint32_t t_p = tmem_base + kColP;
       const uint32_t t_o = tmem_base + kColO;
       bool ok = true;
-      SAGE_WAIT_OR(q_full, 0, 2, ok = false);
+
+      auto issue_qk = [&](int stage, int h) {
+        const uint64_t desc_k =
+            umma_smem_desc(smem_u32(s_k + stage * L::kKBytes + h * kHalfKBytes), 16, kSboQK, kSwzQK);
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) {             // 32 int8 of head_dim per instruction
+          mma_i8_ss(tmem_base + kColS + h * kHalfN, desc_q + 2 * k, desc_k + 2 * k, kIdescQK, k > 0 ? 1u : 0u);
+        }
+        tc_commit(s_full + h);
+      };
+
+      SAGE_WAIT_OR(q_full, 0, 3, ok = false);
+      if (ok) SAGE_WAIT_OR(k_full, 0, 4, ok = false);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0);
+        issue_qk(0, 1);
+        tc_commit(k_empty);                          // K(0) is consumed once QK(0,1) is done
+      }
 #pragma unroll 1
       for (int j = 0; ok && j < n_kv; ++j) {
         const int s = j % kStages;
         const uint32_t ph = (j / kStages) & 1;
-        SAGE_WAIT_OR(k_full + s, ph, 3, break);
-        tc_fence_after();
-        const uint64_t desc_k = umma_smem_desc(smem_u32(s_k + s * L::kKBytes), 16, kSboQK, kSwzQK);
+        const int s1 = (j + 1) % kStages;
+        const uint32_t ph1 = ((j + 1) / kStages) & 1;
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) {             // 32 int8 of head_dim per instruction
-          mma_i8_ss(t_s, desc_q + 2 * k, desc_k + 2 * k, kIdescQK, k > 0 ? 1u : 0u);
-        }
-        tc_commit(s_full);
-        SAGE_WAIT_OR(p_full, j & 1, 4, break);
-        SAGE_WAIT_OR(v_full + s, ph, 5, break);
-        tc_fence_after();
-        // V tile: [128 kv rows][64 fp16] blocks of 16 KB, one per 64 columns of head_dim
-        const uint64_t desc_v =
-            umma_smem_desc(smem_u32(s_v + s * L::kVBytes), kBlockN * 128, 1024, kSwizzle128B);
+        for (int h = 0; h < 2; ++h) {
+          SAGE_WAIT_OR(p_full + h, j & 1, 5, { ok = false; break; });
+          if (h == 0) SAGE_WAIT_OR(v_full + s, ph, 6, { ok = false; break; });
+          tc_fence_after();
+          // V tile: [128 kv rows][64 fp16] blocks of 16 KB, one per 64 columns of head_dim;
+          // half h starts 64 rows = 8192 bytes in, each instruction takes 16 rows = 2048 bytes.
+          const uint64_t desc_v =
+              umma_smem_desc(smem_u32(s_v + s * L::kVBytes + h * (kHalfN * 128)), kBlockN * 128, 1024, kSwizzle128B);
 #pragma unroll
-        for (int k = 0; k < kBlockN / 16; ++k) {       // 16 kv rows per instruction = 2048 bytes
-          mma_f16_ts(t_o, t_p + 8 * k, desc_v + 128 * k, kIdescPV, (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kHalfN / 16; ++k) {
+            mma_f16_ts(t_o, tmem_base + kColP + h * kHalfN + 8 * k, desc_v + 128 * k, kIdescPV,
+                       (j > 0 || h > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(pv_done + h);
+          if (h == 1) tc_commit(v_empty + s);
+          if (j + 1 < n_kv) {
+            if (h == 0) SAGE_WAIT_OR(k_full + s1, ph1, 7, { ok = false; break; });
+            tc_fence_after();
+            issue_qk(s1, h);
+            if (h == 1) tc_commit(k_empty + s1);   // K(j+1) is consumed once QK(j+1,1) is done
+          }
         }
-        tc_commit(kv_empty + s);
       }
       tc_commit(o_final);
     }
@@ -234,75 +298,91 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // ------------------------------------------------------------------ softmax / epilogue
     const int row = q_base + threadIdx.x;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_base + kColS;
-    const uint32_t t_p = tmem_base + lane_base + kColP;
     const uint32_t t_o = tmem_base + lane_base + kColO;
     const int q_grp = (q_base + warp * 32) / 32;
     const float qs = (q_grp < p.q_groups) ? __ldg(p.q_scale + static_cast<long long>(bh) * p.q_groups + q_grp) : 0.0f;
     const float* ks_base = p.k_scale + static_cast<long long>(b * p.Hkv + hkv) * p.k_groups;
 
     float m_used = kMaskValue;
-    float l = 0.0f;
+    float2 l2 = make_float2(0.0f, 0.0f);
     bool ok = true;
 
-#pragma unroll 1
-    for (int j = 0; j < n_kv; ++j) {
-      const int kv_base = j * kBlockN;
-      SAGE_WAIT_OR(s_full, j & 1, 6, { ok = false; break; });
-      tc_fence_after();
-      uint32_t sr[4][32];
+    // k_scale of the next half is fetched one half ahead, off the critical path
+    float ks_next[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + 32 * c, sr[c]);
+    for (int g = 0; g < 4; ++g) ks_next[g] = (g < p.k_groups) ? __ldg(ks_base + g) : 0.0f;
+
+    const int n_half = 2 * n_kv;
+#pragma unroll 1
+    for (int hh = 0; hh < n_half; ++hh) {
+      const int j = hh >> 1;
+      const int h = hh & 1;
+      const int kv_base = hh * kHalfN;
+      const uint32_t t_s = tmem_base + lane_base + kColS + h * kHalfN;
+
+      float cg[4];                                      // q_scale * k_scale per 16 columns (:621)
+#pragma unroll
+      for (int g = 0; g < 4; ++g) cg[g] = __fmul_rn(qs, ks_next[g]);
+
+      SAGE_WAIT_OR(s_full + h, j & 1, 8, { ok = false; break; });
+      tc_fence_after();
+      uint32_t sr[2][32];
+      tmem_ld32(t_s, sr[0]);
+      tmem_ld32(t_s + 32, sr[1]);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int kg = (kv_base + kHalfN) / 16 + g;
+        ks_next[g] = (kg < p.k_groups) ? __ldg(ks_base + kg) : 0.0f;
+      }
       tc_wait_ld();
 
       if (p.s_dump != nullptr && row < p.Sq) {
         int32_t* dst = p.s_dump + (static_cast<long long>(bh) * p.Sq + row) * p.Skv + kv_base;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (kv_base + 32 * c + i < p.Skv) dst[32 * c + i] = static_cast<int32_t>(sr[c][i]);
       }
 
-      float cg[8];                                      // q_scale * k_scale per 16 columns (:621)
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const int kg = kv_base / 16 + g;
-        cg[g] = (kg < p.k_groups) ? __fmul_rn(qs, __ldg(ks_base + kg)) : 0.0f;
-      }
-
-      const bool masked_tile = (CAUSAL && kv_base + kBlockN - 1 > q_base) || (kv_base + kBlockN > p.Skv);
+      const bool masked = (CAUSAL && kv_base + kHalfN - 1 > q_base) || (kv_base + kHalfN > p.Skv);
       // columns below this bound are visible to this row (causal: col <= row; length: col < Skv)
-      const int col_end = masked_tile ? min(p.Skv, CAUSAL ? row + 1 : p.Skv) - kv_base : kBlockN;
+      const int col_end = masked ? min(p.Skv, CAUSAL ? row + 1 : p.Skv) - kv_base : kHalfN;
 
-      float m_tile = kMaskValue;
-      if (!masked_tile) {
+      float m_half = kMaskValue;
+      if (!masked) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {                   // scales are >= 0: max commutes with the scaling
+        for (int g = 0; g < 4; ++g) {                   // scales are >= 0: max commutes with the scaling
           int mx = static_cast<int>(sr[g >> 1][(g & 1) * 16]);
 #pragma unroll
           for (int i = 1; i < 16; ++i) mx = max(mx, static_cast<int>(sr[g >> 1][(g & 1) * 16 + i]));
-          m_tile = fmaxf(m_tile, __int2float_rn(mx) * cg[g]);
+          m_half = fmaxf(m_half, __int2float_rn(mx) * cg[g]);
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float sv = __int2float_rn(static_cast<int>(sr[c][i])) * cg[(32 * c + i) >> 4];
-            if (32 * c + i < col_end) m_tile = fmaxf(m_tile, sv);
+            if (32 * c + i < col_end) m_half = fmaxf(m_half, sv);
           }
       }
 
       // lazy rescale: move the running maximum only when it grew by more than 2^8
-      if (j == 0) {
-        m_used = m_tile;
+      if (hh == 0) {
+        m_used = m_half;
       } else {
-        const bool need = m_tile > m_used + kLazyRescaleLog2;
+        const bool need = m_half > m_used + kLazyRescaleLog2;
         if (__any_sync(0xffffffffu, need)) {
-          const float alpha = need ? fast_exp2(m_used - m_tile) : 1.0f;   // (:667)
-          if (need) m_used = m_tile;
-          l *= alpha;
+          // O must be at rest: the P.V of the previous half has to be complete
+          const int hp = h ^ 1;
+          const int jp = (hh - 1) >> 1;
+          SAGE_WAIT_OR(pv_done + hp, jp & 1, 9, { ok = false; break; });
+          tc_fence_after();
+          const float alpha = need ? fast_exp2(m_used - m_half) : 1.0f;   // (:667)
+          if (need) m_used = m_half;
+          l2.x *= alpha;
+          l2.y *= alpha;
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
             uint32_t orr[32];
@@ -316,35 +396,36 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
 
       // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs back into TMEM
-      float l_add0 = 0.0f, l_add1 = 0.0f;
+      const float2 neg_m = make_float2(-m_used, -m_used);
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int e = 32 * c + 2 * i;
           const float cs = cg[e >> 4];
-          float p0 = fast_exp2(fmaf(__int2float_rn(static_cast<int>(sr[c][2 * i])), cs, -m_used));
-          float p1 = fast_exp2(fmaf(__int2float_rn(static_cast<int>(sr[c][2 * i + 1])), cs, -m_used));
-          if (masked_tile) {
-            if (e >= col_end) p0 = 0.0f;
-            if (e + 1 >= col_end) p1 = 0.0f;
+          const float2 sf = make_float2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
+                                        __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
+          const float2 x = ffma2(sf, make_float2(cs, cs), neg_m);
+          float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          if (masked) {
+            if (e >= col_end) pp.x = 0.0f;
+            if (e + 1 >= col_end) pp.y = 0.0f;
           }
-          l_add0 += p0;
-          l_add1 += p1;
-          pk[i] = pack_half2(p0, p1);
+          l2 = fadd2(l2, pp);
+          pk[16 * c + i] = pack_half2(pp.x, pp.y);
         }
-        tmem_st16(t_p + 16 * c, pk);
       }
-      l += l_add0 + l_add1;
+      tmem_st32(tmem_base + lane_base + kColP + h * kHalfN, pk);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full + h);
     }
+    const float l = l2.x + l2.y;
 
     // ---- epilogue: o = acc * (1/l), one rounding to the output type (:769-786)
     if (ok && n_kv > 0) {
-      SAGE_WAIT_OR(o_final, 0, 7, ok = false);
+      SAGE_WAIT_OR(o_final, 0, 10, ok = false);
       tc_fence_after();
     }
     if (ok) {

@@ -58,108 +58,129 @@ __device__ __forceinline__ int quantise_one(float y) {
   return r;
 }
 
-// One warp quantises one group of ROWS consecutive rows (all D columns) of one (b,h).
-// A row is D/8 lanes x 16 bytes, so a warp reads 32*8/D rows per 512-byte load.
-template <typename T, int D, int ROWS>
-__device__ __forceinline__ void quantise_group(const T* __restrict__ in_bh, long long stride_s, int row0, int S,
-                                               int8_t* __restrict__ out_bh, float* __restrict__ scale_out,
-                                               float s_mul, const T* __restrict__ mean_bh, int lane) {
-  constexpr int kLanesPerRow = D / 8;
-  constexpr int kRowsPerPass = 32 / kLanesPerRow;
-  constexpr int kPasses = ROWS / kRowsPerPass;
-  const int sub = lane / kLanesPerRow;
-  const int col = (lane % kLanesPerRow) * 8;
-
-  float mean8[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) mean8[i] = 0.0f;
-  if (mean_bh != nullptr) {
-    const uint4 mraw = *reinterpret_cast<const uint4*>(mean_bh + col);
-    const T* mv = reinterpret_cast<const T*>(&mraw);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) mean8[i] = elem_to_float<T>(mv[i]);
-  }
-
-  uint4 raw[kPasses];
-#pragma unroll
-  for (int p = 0; p < kPasses; ++p) {
-    const int row = row0 + p * kRowsPerPass + sub;
-    raw[p] = make_uint4(0u, 0u, 0u, 0u);
-    if (row < S) raw[p] = __ldg(reinterpret_cast<const uint4*>(in_bh + static_cast<long long>(row) * stride_s + col));
-  }
-
-  // pass 1 (csrc/attn_gfx11.cu:189-237): group abs-max of (x - mean)
-  float vmax = 0.0f;
-#pragma unroll
-  for (int p = 0; p < kPasses; ++p) {
-    const int row = row0 + p * kRowsPerPass + sub;
-    if (row < S) {
-      const T* xv = reinterpret_cast<const T*>(&raw[p]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float v = __fsub_rn(elem_to_float<T>(xv[i]), mean8[i]);
-        vmax = fmaxf(vmax, fabsf(v));
-      }
-    }
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
-
-  const float amax = fmaxf(1e-7f, __fmul_rn(vmax, fabsf(s_mul)));      // :192,224
-  if (lane == 0) *scale_out = __fdiv_rn(amax, 127.0f);                 // :244-245
-  const float iscale = __fmul_rn(__fdiv_rn(127.0f, amax), s_mul);      // :252,296
-
-  // pass 2 (csrc/attn_gfx11.cu:250-318): quantise from the registers, 8 bytes per lane and row
-#pragma unroll
-  for (int p = 0; p < kPasses; ++p) {
-    const int row = row0 + p * kRowsPerPass + sub;
-    if (row < S) {
-      const T* xv = reinterpret_cast<const T*>(&raw[p]);
-      uint32_t packed[2] = {0u, 0u};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float v = __fsub_rn(elem_to_float<T>(xv[i]), mean8[i]);
-        const int qv = quantise_one(__fmul_rn(v, iscale));
-        packed[i >> 2] |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * (i & 3));
-      }
-      *reinterpret_cast<uint2*>(out_bh + static_cast<long long>(row) * D + col) = make_uint2(packed[0], packed[1]);
-    }
-  }
-}
+// One warp handles 16 consecutive rows (all D columns) of one (b,h): a K group, or half of a Q
+// group (the two warps of a Q group exchange their maxima through shared memory).  A row is D/8
+// lanes x 16 bytes, so a warp reads 32*8/D rows per 512-byte load and keeps 16*D*2/32 bytes in
+// registers between the max pass and the quantisation pass.
+constexpr int kRowsPerWarp = 16;
+constexpr int kQGroupsPerBlock = kPrepWarps / 2;
+constexpr int kKGroupsPerBlock = kPrepWarps;
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kPrepThreads) sage_prep_kernel(const PrepParams p) {
+struct RowSlab {
+  static constexpr int kLanesPerRow = D / 8;
+  static constexpr int kRowsPerPass = 32 / kLanesPerRow;
+  static constexpr int kPasses = kRowsPerWarp / kRowsPerPass;
+  uint4 raw[kPasses];
+  float mean8[8];
+  int sub, col;
+
+  __device__ __forceinline__ void load(const T* __restrict__ in_bh, long long stride_s, int row0, int S,
+                                       const T* __restrict__ mean_bh, int lane) {
+    sub = lane / kLanesPerRow;
+    col = (lane % kLanesPerRow) * 8;
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const int row = row0 + p * kRowsPerPass + sub;
+      raw[p] = make_uint4(0u, 0u, 0u, 0u);
+      if (row < S) raw[p] = __ldg(reinterpret_cast<const uint4*>(in_bh + static_cast<long long>(row) * stride_s + col));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mean8[i] = 0.0f;
+    if (mean_bh != nullptr) {
+      const uint4 mraw = __ldg(reinterpret_cast<const uint4*>(mean_bh + col));
+      const T* mv = reinterpret_cast<const T*>(&mraw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mean8[i] = elem_to_float<T>(mv[i]);
+    }
+  }
+
+  // pass 1 (csrc/attn_gfx11.cu:189-237): abs-max of (x - mean) over the warp's rows
+  __device__ __forceinline__ float abs_max(int row0, int S) const {
+    float vmax = 0.0f;
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const int row = row0 + p * kRowsPerPass + sub;
+      if (row < S) {
+        const T* xv = reinterpret_cast<const T*>(&raw[p]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(__fsub_rn(elem_to_float<T>(xv[i]), mean8[i])));
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+    return vmax;
+  }
+
+  // pass 2 (csrc/attn_gfx11.cu:250-318): quantise from the registers, 8 bytes per lane and row
+  __device__ __forceinline__ void quantise(int row0, int S, float iscale, int8_t* __restrict__ out_bh) const {
+#pragma unroll
+    for (int p = 0; p < kPasses; ++p) {
+      const int row = row0 + p * kRowsPerPass + sub;
+      if (row < S) {
+        const T* xv = reinterpret_cast<const T*>(&raw[p]);
+        uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float v = __fsub_rn(elem_to_float<T>(xv[i]), mean8[i]);
+          const int qv = quantise_one(__fmul_rn(v, iscale));
+          packed[i >> 2] |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * (i & 3));
+        }
+        *reinterpret_cast<uint2*>(out_bh + static_cast<long long>(row) * D + col) = make_uint2(packed[0], packed[1]);
+      }
+    }
+  }
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPrepThreads, 3) sage_prep_kernel(const PrepParams p) {
+  __shared__ float warp_max[kPrepWarps];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   int blk = blockIdx.x;
 
-  if (blk < p.q_blocks) {                                   // ---- Q groups, one per warp
-    const long long g = static_cast<long long>(blk) * kPrepWarps + warp;
+  if (blk < p.q_blocks) {                                   // ---- Q: a group of 32 rows per warp pair
+    const long long g = static_cast<long long>(blk) * kQGroupsPerBlock + (warp >> 1);
     const long long total = static_cast<long long>(p.B) * p.Hq * p.q_groups;
-    if (g >= total) return;
-    const int grp = static_cast<int>(g % p.q_groups);
-    const int bh = static_cast<int>(g / p.q_groups);
+    const bool valid = g < total;
+    const int grp = valid ? static_cast<int>(g % p.q_groups) : 0;
+    const int bh = valid ? static_cast<int>(g / p.q_groups) : 0;
     const int b = bh / p.Hq, h = bh % p.Hq;
+    const int row0 = grp * kQGroupRows + (warp & 1) * kRowsPerWarp;
+    const int S = valid ? p.Sq : 0;
     const T* in_bh = reinterpret_cast<const T*>(p.q.ptr) + b * p.q.stride_b + h * p.q.stride_h;
-    quantise_group<T, D, kQGroupRows>(in_bh, p.q.stride_s, grp * kQGroupRows, p.Sq,
-                                      p.q_i8 + static_cast<long long>(bh) * p.Sq * D, p.q_scale + g,
-                                      p.sm_scale_log2e, nullptr, lane);
+    RowSlab<T, D> slab;
+    slab.load(in_bh, p.q.stride_s, row0, S, nullptr, lane);
+    const float mine = slab.abs_max(row0, S);
+    if (lane == 0) warp_max[warp] = mine;
+    __syncthreads();
+    const float vmax = fmaxf(warp_max[warp], warp_max[warp ^ 1]);
+    const float s_mul = p.sm_scale_log2e;
+    const float amax = fmaxf(1e-7f, __fmul_rn(vmax, fabsf(s_mul)));      // :192,224
+    if (valid && lane == 0 && (warp & 1) == 0) p.q_scale[g] = __fdiv_rn(amax, 127.0f);   // :244-245
+    const float iscale = __fmul_rn(__fdiv_rn(127.0f, amax), s_mul);      // :252,296
+    slab.quantise(row0, S, iscale, p.q_i8 + static_cast<long long>(bh) * p.Sq * D);
     return;
   }
   blk -= p.q_blocks;
-  if (blk < p.k_blocks) {                                   // ---- K groups, one per warp
-    const long long g = static_cast<long long>(blk) * kPrepWarps + warp;
+  if (blk < p.k_blocks) {                                   // ---- K: a group of 16 rows per warp
+    const long long g = static_cast<long long>(blk) * kKGroupsPerBlock + warp;
     const long long total = static_cast<long long>(p.B) * p.Hkv * p.k_groups;
     if (g >= total) return;
     const int grp = static_cast<int>(g % p.k_groups);
     const int bh = static_cast<int>(g / p.k_groups);
     const int b = bh / p.Hkv, h = bh % p.Hkv;
+    const int row0 = grp * kKGroupRows;
     const T* in_bh = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h;
     const T* mean_bh =
         p.k_mean ? reinterpret_cast<const T*>(p.k_mean) + static_cast<long long>(bh) * D : nullptr;
-    quantise_group<T, D, kKGroupRows>(in_bh, p.k.stride_s, grp * kKGroupRows, p.Skv,
-                                      p.k_i8 + static_cast<long long>(bh) * p.Skv * D, p.k_scale + g, 1.0f,
-                                      mean_bh, lane);
+    RowSlab<T, D> slab;
+    slab.load(in_bh, p.k.stride_s, row0, p.Skv, mean_bh, lane);
+    const float vmax = slab.abs_max(row0, p.Skv);
+    const float amax = fmaxf(1e-7f, vmax);                               // s = 1 for K
+    if (lane == 0) p.k_scale[g] = __fdiv_rn(amax, 127.0f);
+    const float iscale = __fdiv_rn(127.0f, amax);
+    slab.quantise(row0, p.Skv, iscale, p.k_i8 + static_cast<long long>(bh) * p.Skv * D);
     return;
   }
   blk -= p.k_blocks;

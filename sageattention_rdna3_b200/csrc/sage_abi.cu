@@ -183,8 +183,8 @@ int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const v
   p.sm_scale_log2e = s * l2e;
   const long long qg = static_cast<long long>(B) * Hq * p.q_groups;
   const long long kg = static_cast<long long>(B) * Hkv * p.k_groups;
-  p.q_blocks = static_cast<int>((qg + sage::kPrepWarps - 1) / sage::kPrepWarps);
-  p.k_blocks = static_cast<int>((kg + sage::kPrepWarps - 1) / sage::kPrepWarps);
+  p.q_blocks = static_cast<int>((qg + sage::kQGroupsPerBlock - 1) / sage::kQGroupsPerBlock);
+  p.k_blocks = static_cast<int>((kg + sage::kKGroupsPerBlock - 1) / sage::kKGroupsPerBlock);
   const int v_blocks = do_v ? v_block_count(B, Hkv, Skv, D) : 0;
   return dispatch_prep(dtype, D, p, v_blocks, static_cast<cudaStream_t>(stream));
 }

@@ -1,0 +1,115 @@
+"""Multi-GPU sharding of ``sageattn`` over (batch, kv-head) units.
+
+Every (batch, kv head) pair - with the ``Hq/Hkv`` query heads that read it (GQA,
+``csrc/attn_gfx11.cu:464`` of the reference) - is an independent attention problem, so the path
+shards with no exchange during compute.  The reference itself is single-GPU; this module is the
+new piece: a planner (pure Python), slicing of the inputs into a rank's units, and an optional
+final all-gather of the outputs (NCCL on GPUs; any ``torch.distributed`` backend works, the CPU
+tests use gloo).  One process per GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+
+
+@dataclass(frozen=True)
+class Shard:
+    rank: int
+    unit_start: int      # first unit u = b * Hkv + hkv owned by the rank
+    unit_stop: int       # one past the last
+
+    @property
+    def n_units(self) -> int:
+        return self.unit_stop - self.unit_start
+
+
+def plan_shards(batch: int, num_qo_heads: int, num_kv_heads: int, world_size: int) -> List[Shard]:
+    """Contiguous, count-balanced ranges of units per rank (all units cost the same, causal or not).
+
+    The first ``n % world`` ranks get one unit more.  Ranks may be left without work when there are
+    fewer units than ranks.
+    """
+    if batch < 0 or num_kv_heads <= 0 or num_qo_heads % num_kv_heads != 0 or world_size <= 0:
+        raise ValueError("plan_shards: need batch >= 0, Hkv > 0, Hq % Hkv == 0, world_size > 0")
+    n = batch * num_kv_heads
+    base, extra = divmod(n, world_size)
+    shards, start = [], 0
+    for r in range(world_size):
+        size = base + (1 if r < extra else 0)
+        shards.append(Shard(r, start, start + size))
+        start += size
+    return shards
+
+
+def to_units(x: torch.Tensor, tensor_layout: str, num_kv_heads: int) -> torch.Tensor:
+    """View ``x`` ([B,H,S,D] or [B,S,H,D]) as ``[B*Hkv, H/Hkv, S, D]`` (units first, HND inside)."""
+    if tensor_layout == "NHD":
+        x = x.permute(0, 2, 1, 3)
+    B, H, S, D = x.shape
+    rep = H // num_kv_heads
+    return x.reshape(B * num_kv_heads, rep, S, D) if x.is_contiguous() else \
+        x.unflatten(1, (num_kv_heads, rep)).flatten(0, 1)
+
+
+def shard_inputs(q, k, v, tensor_layout: str, shard: Shard):
+    """This rank's units as a batch of single-kv-head problems in HND layout:
+    q ``[n, Hq/Hkv, Sq, D]``, k and v ``[n, 1, Skv, D]``."""
+    hkv = k.size(1) if tensor_layout == "HND" else k.size(2)
+    sl = slice(shard.unit_start, shard.unit_stop)
+    return (to_units(q, tensor_layout, hkv)[sl].contiguous(), to_units(k, tensor_layout, hkv)[sl].contiguous(),
+            to_units(v, tensor_layout, hkv)[sl].contiguous())
+
+
+def from_units(o_units: torch.Tensor, batch: int, num_qo_heads: int, tensor_layout: str) -> torch.Tensor:
+    """Inverse of :func:`to_units` for the output: ``[B*Hkv, rep, S, D]`` -> caller layout."""
+    n, rep, S, D = o_units.shape
+    o = o_units.reshape(batch, num_qo_heads, S, D)
+    return o if tensor_layout == "HND" else o.permute(0, 2, 1, 3).contiguous()
+
+
+def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                     is_causal: bool = False, sm_scale: Optional[float] = None, smooth_k: bool = False,
+                     group=None, gather: bool = True, attn_fn: Optional[Callable] = None):
+    """Run this rank's share of ``sageattn(q, k, v)`` and optionally all-gather the outputs.
+
+    Every rank passes the same global ``q, k, v`` (or at least its own units filled in).  Returns the
+    full output in the caller's layout when ``gather`` is true, otherwise this rank's units
+    ``[n, Hq/Hkv, Sq, D]`` and its :class:`Shard`.  ``attn_fn`` defaults to :func:`sageattn`.
+    """
+    import torch.distributed as dist
+    if attn_fn is None:
+        from .core import sageattn as attn_fn
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    B = q.size(0)
+    hq = q.size(1) if tensor_layout == "HND" else q.size(2)
+    hkv = k.size(1) if tensor_layout == "HND" else k.size(2)
+    shards = plan_shards(B, hq, hkv, world)
+    mine = shards[rank]
+    ql, kl, vl = shard_inputs(q, k, v, tensor_layout, mine)
+    if mine.n_units > 0:
+        o_local = attn_fn(ql, kl, vl, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k)
+    else:
+        o_local = ql.new_empty(ql.shape)
+    if not gather:
+        return o_local, mine
+    if world == 1:
+        return from_units(o_local, B, hq, tensor_layout)
+    rep, Sq, D = hq // hkv, ql.size(2), ql.size(3)
+    sizes = [s.n_units for s in shards]
+    if len(set(sizes)) == 1:
+        # equal slabs of [units, rep, Sq, D]: one all_gather_into_tensor straight into the result
+        out = o_local.new_empty(B * hkv, rep, Sq, D)
+        dist.all_gather_into_tensor(out, o_local.contiguous(), group=group)
+    else:
+        # unequal shares: pad every rank's slab to the largest, gather, drop the padding
+        n_max = max(sizes)
+        padded = o_local.new_zeros(n_max, rep, Sq, D)
+        padded[:mine.n_units] = o_local
+        gathered = o_local.new_empty(world * n_max, rep, Sq, D)
+        dist.all_gather_into_tensor(gathered, padded, group=group)
+        out = torch.cat([gathered[r * n_max:r * n_max + n] for r, n in enumerate(sizes)], dim=0)
+    return from_units(out, B, hq, tensor_layout)
