@@ -1,0 +1,337 @@
+"""GPU parity tests (need a B200).  The CUDA path is called through the C ABI (ctypes) and through
+the public ``sageattn``; the checker is the CPU oracle on the same seeded inputs.
+
+Bars: int8 values, fp32 scales, K mean and int32 Q.K^T are bit-exact; the attention output reaches
+cosine >= 0.999 and relative L1 <= 1e-2 against the oracle, and stays inside the reference's own
+gates against fp32 SDPA (cosine > 0.99 fp16 / 0.98 bf16, max-abs < 0.35; test_sageattn_rdna3.py:39-53).
+"""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+
+import helpers as H  # noqa: E402
+from cases import CASES, make_case  # noqa: E402
+from oracle import sage_oracle as so  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+COS_MIN, REL_L1_MAX = 0.999, 1e-2       # kernel vs oracle (the north-star tolerance)
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from sageattention_rdna3_b200 import _native
+    _native.load_ops()                   # fails loudly if the extension is missing
+    return torch.device("cuda", 0)
+
+
+def shapes(B, Hq, Hkv, Sq, Skv, D, layout):
+    f = (lambda h, s: (B, h, s, D)) if layout == "HND" else (lambda h, s: (B, s, h, D))
+    return f(Hq, Sq), f(Hkv, Skv)
+
+
+def bits_equal(a, b):
+    if a.dtype in (torch.float32,):
+        return torch.equal(a.cpu().view(torch.int32), b.cpu().view(torch.int32))
+    if a.dtype in (torch.float16, torch.bfloat16):
+        return torch.equal(a.cpu().contiguous().view(torch.int16), b.cpu().contiguous().view(torch.int16))
+    return torch.equal(a.cpu(), b.cpu())
+
+
+def outliers(x, seed, frac=0.01, gain=20.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.where(torch.rand(x.shape, generator=g) < frac, x.float() * gain, x.float()).to(x.dtype)
+
+
+QUANT_CASES = [
+    # B, Hq, Hkv, Sq, Skv, D, dtype, layout, smooth_k, sm_scale, k_offset, with_outliers
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, None, 0.0, False),      # BASELINE config 1
+    (1, 10, 10, 4096, 4096, 64, torch.float16, "NHD", False, None, 0.0, False),    # config 2 (full size)
+    (1, 2, 2, 8192, 8192, 128, torch.bfloat16, "HND", True, None, 2.5, False),     # config 3, two heads
+    (1, 4, 1, 4096, 4096, 128, torch.bfloat16, "HND", False, None, 0.0, True),     # config 4, one GQA unit
+    (1, 1, 1, 4096, 4096, 128, torch.float16, "NHD", False, None, 0.0, False),     # config 5 shape, trimmed S
+    (2, 4, 2, 300, 333, 128, torch.bfloat16, "NHD", True, None, 1.5, False),
+    (1, 3, 3, 33, 65, 64, torch.bfloat16, "HND", True, 0.5, -1.0, False),
+    (1, 2, 2, 1, 1, 64, torch.float16, "HND", False, None, 0.0, False),
+    (1, 2, 2, 1057, 17, 128, torch.float16, "HND", True, None, 0.3, False),
+]
+
+
+@pytest.mark.parametrize("case", QUANT_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_quant_and_mean_bit_exact(dev, case):
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, smooth, sm, k_off, outl = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k, v = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype, offset=k_off), H.randn(sk, 2, dtype)
+    if outl:
+        q, k = outliers(q, 3), outliers(k, 4)
+    sm = D ** -0.5 if sm is None else sm
+    qh, kh, vh = so.to_hnd(q, layout), so.to_hnd(k, layout), so.to_hnd(v, layout)
+    mean_ref = so.mean_seq(kh) if smooth else None
+    ref = so.quant_qk_int8(qh, kh, mean_ref, sm)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    mean = H.abi_mean_seq(kd, layout) if smooth else None
+    if smooth:
+        assert bits_equal(mean, mean_ref), "K mean differs"
+    q_i8, q_scale, k_i8, k_scale, v16 = H.abi_quant(qd, kd, mean, layout, sm, v=vd)
+    torch.cuda.synchronize()
+    assert bits_equal(q_scale, ref[1]), "q_scale differs"
+    assert bits_equal(k_scale, ref[3]), "k_scale differs"
+    assert bits_equal(q_i8, ref[0]), f"q_int8 differs in {(q_i8.cpu() != ref[0]).sum().item()} places"
+    assert bits_equal(k_i8, ref[2]), f"k_int8 differs in {(k_i8.cpu() != ref[2]).sum().item()} places"
+    assert bits_equal(v16, so.v_to_f16(vh).contiguous()), "fp16 copy of V differs"
+    assert bits_equal(H.abi_v_to_f16(vd, layout), so.v_to_f16(vh).contiguous())
+
+
+ATTN_CASES = [
+    # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal
+    (1, 1, 1, 128, 128, 128, torch.float16, "HND", False),
+    (1, 1, 1, 128, 128, 64, torch.float16, "HND", False),
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False),         # BASELINE config 1
+    (1, 2, 2, 256, 384, 128, torch.float16, "HND", False),
+    (1, 2, 1, 512, 512, 128, torch.bfloat16, "HND", True),
+    (2, 4, 2, 300, 333, 64, torch.bfloat16, "NHD", True),
+    (1, 2, 2, 100, 1057, 128, torch.float16, "NHD", False),
+    (1, 2, 2, 1057, 100, 64, torch.float16, "HND", True),           # more queries than keys, causal
+    (1, 1, 1, 1, 1, 64, torch.float16, "HND", True),
+    (1, 2, 2, 33, 65, 128, torch.bfloat16, "NHD", False),
+]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_attention_int32_scores_bit_exact_and_output_close(dev, case):
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k, v = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype), H.randn(sk, 2, dtype)
+    sm = D ** -0.5
+    qh, kh, vh = so.to_hnd(q, layout), so.to_hnd(k, layout), so.to_hnd(v, layout)
+    rq = so.quant_qk_int8(qh, kh, None, sm)
+    s_ref = so.qk_int32(rq[0], rq[2])
+    o_ref = so.attention(rq[0], rq[2], so.v_to_f16(vh), rq[1], rq[3], causal, dtype)
+    q_i8, q_scale, k_i8, k_scale, v16 = H.abi_quant(q.to(dev), k.to(dev), None, layout, sm, v=v.to(dev))
+    o, dump, status = H.abi_attn(q_i8, k_i8, v16, "HND", q_scale, k_scale, dtype, layout, causal, dump=True)
+    assert status == 0
+    d = dump.cpu()
+    if causal:      # only the KV tiles a query tile visits are produced: col < min(tile_end, Skv)
+        rows, cols = torch.arange(Sq)[:, None], torch.arange(Skv)[None, :]
+        visited = cols < torch.clamp((rows // 128 + 1) * 128, max=Skv)
+        assert torch.equal(d[..., visited], s_ref[..., visited]), "int32 Q.K^T differs"
+    else:
+        assert torch.equal(d, s_ref), "int32 Q.K^T differs"
+    oh = so.to_hnd(o.cpu(), layout)
+    assert not torch.isnan(oh.float()).any(), "output has unwritten (NaN-filled) elements"
+    acc = so.accuracy(oh.float(), o_ref.float())
+    assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, acc
+
+
+def _public(q, k, v, dev, **kw):
+    from sageattention_rdna3_b200 import check_status, sageattn
+    o = sageattn(q.to(dev), k.to(dev), v.to(dev), **kw)
+    check_status(dev)
+    return o
+
+
+# The reference's 36 operator tests (test_sageattn_rdna3.py:83-287), same shapes; every one runs the
+# INT8 path here.
+REF_OP_CASES = (
+    [(1, 2, 2, S, S, D, torch.float16, "HND", False, False, None) for D in (64, 128) for S in (128, 256, 512, 1024)]
+    + [(1, 2, 2, 2048, 2048, 64, torch.float16, "HND", False, False, None),
+       (1, 2, 2, 1024, 1024, 128, torch.float16, "HND", False, False, None)]
+    + [(2, 4, 4, S, S, 64, torch.float16, "NHD", False, False, None) for S in (128, 512)]
+    + [(1, 4, 4, 256, 256, D, torch.bfloat16, "HND", False, False, None) for D in (64, 128)]
+    + [(1, 2, 2, 256, 256, 64, torch.float16, "HND", False, False, 0.5)]
+    + [(1, 2, 2, 1024, 128, 64, torch.float16, "HND", False, False, None),
+       (1, 2, 2, 512, 2048, 64, torch.float16, "HND", False, False, None)]
+    + [(1, 2, 2, S, S, 64, torch.float16, "HND", True, False, None) for S in (128, 256, 512, 2048)]
+    + [(1, 4, 2, 256, 256, 64, torch.float16, "HND", False, False, None),
+       (1, 8, 2, 256, 256, 128, torch.float16, "HND", False, False, None)]
+    + [(1, 2, 2, 512, 512, 64, torch.float16, "HND", False, sk, None) for sk in (True, False)]
+    + [(1, 2, 2, 32, 32, 64, torch.float16, "HND", False, False, None)]
+    + [(1, 2, 2, S, S, 64, torch.float16, "HND", False, False, None) for S in (33, 65, 100, 127, 129, 255, 1057)]
+    + [(1, 1, 1, 256, 256, 64, torch.float16, "HND", False, False, None)]
+)
+
+
+@pytest.mark.parametrize("case", REF_OP_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_sageattn_reference_cases_vs_sdpa_and_oracle(dev, case):
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth, sm = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k, v = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype), H.randn(sk, 2, dtype)
+    o = _public(q, k, v, dev, tensor_layout=layout, is_causal=causal, sm_scale=sm, smooth_k=smooth)
+    assert o.shape == q.shape and o.dtype == dtype
+    o = o.cpu()
+    ref = so.sdpa_fp32(q, k, v, tensor_layout=layout, is_causal=causal, sm_scale=sm)
+    acc = so.accuracy(o.float(), ref)
+    assert acc["cos"] > (0.99 if dtype == torch.float16 else 0.98), acc
+    assert acc["max_abs"] < 0.35, acc
+    emu = so.sageattn_emulated(q, k, v, tensor_layout=layout, is_causal=causal, sm_scale=sm, smooth_k=smooth)
+    acc2 = so.accuracy(o.float(), emu.float())
+    assert acc2["cos"] >= COS_MIN and acc2["rel_l1"] <= REL_L1_MAX, acc2
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_gpu_matches_golden_fixtures(dev, name):
+    spec = CASES[name]
+    q, k, v = make_case(spec)
+    layout, sm = spec["layout"], spec.get("sm_scale") or spec["D"] ** -0.5
+    gold = np.load(os.path.join(HERE, "golden", f"{name}.npz"))
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    mean = H.abi_mean_seq(kd, layout) if spec["smooth_k"] else None
+    if mean is not None:
+        assert np.array_equal(mean.cpu().view(torch.int16).numpy(), gold["k_mean_bits"])
+    q_i8, q_scale, k_i8, k_scale, _ = H.abi_quant(qd, kd, mean, layout, sm, v=vd)
+    assert np.array_equal(q_i8.cpu().numpy(), gold["q_i8"]) and np.array_equal(k_i8.cpu().numpy(), gold["k_i8"])
+    assert np.array_equal(q_scale.cpu().numpy().view(np.int32), gold["q_scale"].view(np.int32))
+    assert np.array_equal(k_scale.cpu().numpy().view(np.int32), gold["k_scale"].view(np.int32))
+    o = _public(q, k, v, dev, tensor_layout=layout, is_causal=spec["causal"], sm_scale=spec.get("sm_scale"),
+                smooth_k=spec["smooth_k"]).cpu()
+    o_gold = torch.from_numpy(gold["o_bits"]).view(o.dtype)
+    acc = so.accuracy(o.float(), o_gold.float())
+    assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, acc
+
+
+# ----------------------------------------------------------------------------------------------
+# BASELINE sizes.  The oracle cannot do the whole of configs 3-5 in seconds, so: (a) full-size
+# launches are checked through size-independent properties, (b) whole (batch, kv-head) units or row
+# blocks of them are compared with the oracle.
+def test_config3_full_size_properties_and_sampled_units(dev):
+    """B=2 H=32 S=8192 D=128 bf16 HND causal smooth_k, K with a per-channel DC offset."""
+    B, Hh, S, D = 2, 32, 8192, 128
+    g = torch.Generator(device="cpu").manual_seed(0)
+    q = torch.randn((B, Hh, S, D), generator=g).to(torch.bfloat16)
+    off = torch.rand((1, Hh, 1, D), generator=g) * 8.0 - 4.0
+    k = (torch.randn((B, Hh, S, D), generator=g) + off).to(torch.bfloat16)
+    v = torch.randn((B, Hh, S, D), generator=g).to(torch.bfloat16)
+    kw = dict(tensor_layout="HND", is_causal=True, smooth_k=True)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    from sageattention_rdna3_b200 import check_status, sageattn
+    o = sageattn(qd, kd, vd, **kw)
+    # (1) softmax rows sum to one: V = 1 gives O = 1
+    ones = sageattn(qd, kd, torch.ones_like(vd), **kw)
+    assert (ones.float() - 1.0).abs().max().item() <= 2 ** -7
+    # (2) causal: the first query row sees only key 0 (V goes through fp16, csrc/attn_gfx11.cu:377-381)
+    assert torch.equal(o[:, :, 0], vd[:, :, 0].to(torch.float16).to(torch.bfloat16))
+    # (3) linear in V, exactly: doubling V doubles every product, sum and the rounded result
+    o2 = sageattn(qd, kd, vd * 2, **kw)
+    assert torch.equal(o2, o * 2)
+    # (4) units are independent: one (batch, head) computed alone equals its slice, bit for bit
+    alone = sageattn(qd[1:2, 5:6].contiguous(), kd[1:2, 5:6].contiguous(), vd[1:2, 5:6].contiguous(), **kw)
+    assert torch.equal(alone, o[1:2, 5:6])
+    check_status(dev)
+    # (5) two whole units against the oracle
+    for (b, h) in ((0, 0), (1, 31)):
+        emu = so.sageattn_emulated(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], is_causal=True,
+                                   smooth_k=True)
+        acc = so.accuracy(o[b:b + 1, h:h + 1].float().cpu(), emu.float())
+        assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, (b, h, acc)
+
+
+def test_config4_gqa_outliers_sampled_unit(dev):
+    """B=4 Hq=32 Hkv=8 S=4096 D=128 bf16 HND causal, 1 % of q/k entries x20."""
+    B, Hq, Hkv, S, D = 4, 32, 8, 4096, 128
+    q = outliers(H.randn((B, Hq, S, D), 0, torch.bfloat16), 3)
+    k = outliers(H.randn((B, Hkv, S, D), 1, torch.bfloat16), 4)
+    v = H.randn((B, Hkv, S, D), 2, torch.bfloat16)
+    o = _public(q, k, v, dev, tensor_layout="HND", is_causal=True).cpu()
+    for (b, hkv) in ((0, 0), (3, 7)):
+        qs = q[b:b + 1, 4 * hkv:4 * hkv + 4]
+        emu = so.sageattn_emulated(qs, k[b:b + 1, hkv:hkv + 1], v[b:b + 1, hkv:hkv + 1], is_causal=True)
+        acc = so.accuracy(o[b:b + 1, 4 * hkv:4 * hkv + 4].float(), emu.float())
+        assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, (b, hkv, acc)
+        ref = so.sdpa_fp32(qs, k[b:b + 1, hkv:hkv + 1], v[b:b + 1, hkv:hkv + 1], is_causal=True)
+        assert so.accuracy(o[b:b + 1, 4 * hkv:4 * hkv + 4].float(), ref)["cos"] > 0.98
+
+
+def test_config5_long_sequence_row_blocks(dev):
+    """B=1 H=24 S=32768 D=128 fp16 NHD non-causal: full launch, oracle on row blocks of two heads."""
+    B, Hh, S, D = 1, 24, 32768, 128
+    q, k, v = (H.randn((B, S, Hh, D), s, torch.float16) for s in (0, 1, 2))
+    o = _public(q, k, v, dev, tensor_layout="NHD").cpu()
+    assert o.shape == (B, S, Hh, D)
+    sm = D ** -0.5
+    for h in (0, 23):
+        kh, vh = k[:, :, h:h + 1].permute(0, 2, 1, 3), v[:, :, h:h + 1].permute(0, 2, 1, 3)
+        for r0 in (0, S - 256):
+            qh = q[:, r0:r0 + 256, h:h + 1].permute(0, 2, 1, 3)
+            rq = so.quant_qk_int8(qh, kh, None, sm)
+            emu = so.attention(rq[0], rq[2], so.v_to_f16(vh), rq[1], rq[3], False, torch.float16)
+            got = o[:, r0:r0 + 256, h:h + 1].permute(0, 2, 1, 3)
+            acc = so.accuracy(got.float(), emu.float())
+            assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, (h, r0, acc)
+    # non-causal attention does not care about the order of the keys, as long as the 16-row
+    # quantisation groups move as a whole: permute K/V in blocks of 16 rows
+    g = torch.Generator(device="cpu").manual_seed(9)
+    perm = (torch.randperm(S // 16, generator=g)[:, None] * 16 + torch.arange(16)[None, :]).flatten()
+    o_perm = _public(q[:, :, :2], k[:, perm][:, :, :2], v[:, perm][:, :, :2], dev, tensor_layout="NHD").cpu()
+    acc = so.accuracy(o_perm.float(), o[:, :, :2].float())
+    assert acc["cos"] >= 0.99999 and acc["rel_l1"] <= 2e-3, acc
+
+
+# ----------------------------------------------------------------------------------------------
+def test_api_contract_details(dev):
+    from sageattention_rdna3_b200 import sageattn, sageattn_qk_int8_pv_fp16_cuda
+    q, k, v = (H.randn((1, 2, 200, 64), s, torch.float32).to(dev) for s in (0, 1, 2))
+    o32 = sageattn(q, k, v)                                   # fp32 in -> fp16 compute -> fp32 out
+    assert o32.dtype == torch.float32
+    o16 = sageattn(q.half(), k.half(), v.half())
+    assert torch.equal(o32, o16.float())
+    o, lse = sageattn(q.half(), k.half(), v.half(), return_lse=True)      # placeholder zeros
+    assert lse.shape == (1, 2, 200) and lse.dtype == torch.float32 and not lse.any()
+    o_kw = sageattn_qk_int8_pv_fp16_cuda(q.half(), k.half(), v.half(), bm_sel=1, pv_accum_dtype="fp32", smooth_k=False)
+    assert torch.equal(o_kw, o16)                             # unknown kwargs are ignored
+    with pytest.raises(AssertionError, match="head_dim"):
+        sageattn(q[..., :32].half(), k[..., :32].half(), v[..., :32].half())
+    with pytest.raises(AssertionError, match="same dtype"):
+        sageattn(q.half(), k.half(), v.bfloat16())
+    with pytest.raises(AssertionError, match="contiguous"):
+        wide = H.randn((1, 2, 200, 128), 3, torch.float16).to(dev)
+        sageattn(wide[..., ::2], wide[..., ::2], wide[..., ::2])
+
+
+def test_strided_and_empty_inputs(dev):
+    from sageattention_rdna3_b200 import check_status, sageattn
+    # k, v as slices of a packed [B, S, 3, H, D] tensor (strides are multiples of 8: no copy needed)
+    qkv = H.randn((1, 300, 3, 2, 64), 0, torch.float16).to(dev)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    o = sageattn(q, k, v, tensor_layout="NHD")
+    want = sageattn(q.contiguous(), k.contiguous(), v.contiguous(), tensor_layout="NHD")
+    assert torch.equal(o, want)
+    # a misaligned view of k / v is copied; a misaligned q is refused like in the reference
+    big = H.randn((1, 2, 301, 64), 1, torch.float16).to(dev)
+    k_odd = torch.as_strided(big, (1, 2, 300, 64), (2 * 301 * 64, 301 * 64, 64, 1), 64)
+    assert torch.equal(sageattn(q.transpose(1, 2).contiguous(), k_odd, k_odd),
+                       sageattn(q.transpose(1, 2).contiguous(), k_odd.contiguous(), k_odd.contiguous()))
+    q_bad = torch.as_strided(H.randn((1, 2, 16, 68), 2, torch.float16).to(dev), (1, 2, 16, 64), (2 * 16 * 68, 16 * 68, 68, 1))
+    with pytest.raises(AssertionError, match="multiples of 8"):
+        sageattn(q_bad, q_bad, q_bad)
+    # no queries / no keys
+    e = sageattn(q[:, :0], k, v, tensor_layout="NHD")
+    assert e.shape == (1, 0, 2, 64)
+    z = sageattn(q, k[:, :0], v[:, :0], tensor_layout="NHD")
+    assert z.shape == q.shape and not z.any()
+    check_status(dev)
+
+
+def test_torch_ops_match_the_c_abi(dev):
+    """torch.ops.sageattention.* is a thin wrapper: same bits as calling the C ABI directly."""
+    from sageattention_rdna3_b200 import _native
+    ops = _native.load_ops()
+    q, k, v = (H.randn((2, 3, 150, 128), s, torch.bfloat16).to(dev) for s in (0, 1, 2))
+    mean = ops.mean_seq(k, 1)
+    assert bits_equal(mean, H.abi_mean_seq(k, "HND"))
+    a = ops.prep_qkv(q, k, v, mean, 1, 0.1)
+    b = H.abi_quant(q, k, mean, "HND", 0.1, v=v)
+    for x, y in zip(a, b):
+        assert bits_equal(x, y)
+    c = ops.quant_qk_int8(q, k, torch.empty(0, device=dev, dtype=q.dtype), 1, 0.1)
+    d = H.abi_quant(q, k, None, "HND", 0.1)
+    for x, y in zip(c, d[:4]):
+        assert bits_equal(x, y)
+    assert bits_equal(ops.v_to_f16(v, 1), b[4])
+    with pytest.raises(RuntimeError, match="head_dim"):
+        ops.quant_qk_int8(q[..., :96].contiguous(), k[..., :96].contiguous(), torch.empty(0, device=dev, dtype=q.dtype), 1, 0.1)

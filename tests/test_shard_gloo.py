@@ -1,0 +1,67 @@
+"""The multi-rank path on CPU: two gloo ranks shard (batch, kv-head) units, each computes its own
+with the CPU oracle standing in for the GPU kernels, and the all-gather must reproduce the
+single-process result exactly."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_attn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=False):
+    from oracle import sage_oracle as so
+    return so.sageattn_emulated(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
+                                smooth_k=smooth_k)
+
+
+def _worker(rank, world, port, layout, B, Hq, Hkv, result_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    torch.set_num_threads(2)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from helpers import randn
+        from sageattention_rdna3_b200.shard import sageattn_sharded
+        S, D = 48, 64
+        shp = (lambda h: (B, h, S, D)) if layout == "HND" else (lambda h: (B, S, h, D))
+        q, k, v = randn(shp(Hq), 0, torch.float16), randn(shp(Hkv), 1, torch.float16), randn(shp(Hkv), 2, torch.float16)
+        out = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, attn_fn=_oracle_attn)
+        local, shard = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True,
+                                        attn_fn=_oracle_attn, gather=False)
+        torch.save({"out": out, "n_local": shard.n_units, "local_shape": tuple(local.shape)},
+                   os.path.join(result_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("layout,B,Hq,Hkv", [("HND", 1, 4, 2), ("NHD", 1, 6, 3)])
+def test_two_ranks_reproduce_single_process(tmp_path, layout, B, Hq, Hkv):
+    world = 2
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, layout, B, Hq, Hkv, str(tmp_path)), nprocs=world, join=True)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import randn
+    S, D = 48, 64
+    shp = (lambda h: (B, h, S, D)) if layout == "HND" else (lambda h: (B, S, h, D))
+    q, k, v = randn(shp(Hq), 0, torch.float16), randn(shp(Hkv), 1, torch.float16), randn(shp(Hkv), 2, torch.float16)
+    want = _oracle_attn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True)
+    units = 0
+    for r in range(world):
+        got = torch.load(os.path.join(str(tmp_path), f"rank{r}.pt"))
+        assert got["out"].shape == want.shape
+        assert torch.equal(got["out"], want), f"rank {r}: gathered output differs"
+        units += got["n_local"]
+    assert units == B * Hkv
