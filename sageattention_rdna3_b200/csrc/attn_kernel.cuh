@@ -25,6 +25,7 @@
 #include <cuda_fp16.h>
 #include <cfloat>
 #include <cstdint>
+#include <type_traits>
 
 #include "ptx_sm100.cuh"
 
@@ -55,6 +56,7 @@ struct AttnParams {
   int B, Hq, Hkv, Sq, Skv;
   int q_groups, k_groups;
   int n_q_tiles;
+  int head_group;               // (batch, head) pairs scheduled together (a multiple of Hq/Hkv)
   int out_bf16;
   int32_t* s_dump;              // optional [B,Hq,Sq,Skv] int32 copy of Q.K^T (debug / parity)
   int* status;                  // optional device word, stays 0 on success
@@ -116,7 +118,7 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
 
 constexpr int kHalfN = kBlockN / 2;      // the softmax works on 64-column halves of a KV tile
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool DUMP>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -127,11 +129,18 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Heaviest (last) query tiles first; neighbouring CTAs are heads of the same batch, so the query
-  // heads of one KV head (GQA) run together and share K/V through L2.
+  // CTA order: (batch, head) pairs are taken `head_group` at a time; within a group the heaviest
+  // (last) query tiles go first and neighbouring CTAs are neighbouring heads.  The CTAs resident at
+  // any moment then read the K/V of a few heads only (they stay in L2), and the query heads of one
+  // KV head (GQA) run together.
   const int n_bh = p.B * p.Hq;
-  const int bh = blockIdx.x % n_bh;
-  const int qt = p.n_q_tiles - 1 - blockIdx.x / n_bh;
+  const int per_group = p.n_q_tiles * p.head_group;
+  const int group = blockIdx.x / per_group;
+  const int g_first = group * p.head_group;
+  const int g_size = min(p.head_group, n_bh - g_first);
+  const int within = blockIdx.x - group * per_group;
+  const int bh = g_first + within % g_size;
+  const int qt = p.n_q_tiles - 1 - within / g_size;
   const int b = bh / p.Hq;
   const int hq = bh % p.Hq;
   const int hkv = hq / (p.Hq / p.Hkv);                              // csrc/attn_gfx11.cu:464
@@ -336,7 +345,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       tc_wait_ld();
 
-      if (p.s_dump != nullptr && row < p.Sq) {
+      if (DUMP && p.s_dump != nullptr && row < p.Sq) {
         int32_t* dst = p.s_dump + (static_cast<long long>(bh) * p.Sq + row) * p.Skv + kv_base;
 #pragma unroll
         for (int c = 0; c < 2; ++c)
@@ -395,27 +404,33 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
 
-      // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs back into TMEM
+      // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs back into TMEM.
+      // Two copies of the loop: only tiles on the diagonal or at the ragged end pay for masking.
       const float2 neg_m = make_float2(-m_used, -m_used);
       uint32_t pk[32];
+      auto exp_pass = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int e = 32 * c + 2 * i;
-          const float cs = cg[e >> 4];
-          const float2 sf = make_float2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
-                                        __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
-          const float2 x = ffma2(sf, make_float2(cs, cs), neg_m);
-          float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-          if (masked) {
-            if (e >= col_end) pp.x = 0.0f;
-            if (e + 1 >= col_end) pp.y = 0.0f;
+          for (int i = 0; i < 16; ++i) {
+            const int e = 32 * c + 2 * i;
+            const float cs = cg[e >> 4];
+            const float2 sf = make_float2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
+                                          __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
+            const float2 x = ffma2(sf, make_float2(cs, cs), neg_m);
+            float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            if constexpr (kMasked) {
+              if (e >= col_end) pp.x = 0.0f;
+              if (e + 1 >= col_end) pp.y = 0.0f;
+            }
+            l2 = fadd2(l2, pp);
+            pk[16 * c + i] = pack_half2(pp.x, pp.y);
           }
-          l2 = fadd2(l2, pp);
-          pk[16 * c + i] = pack_half2(pp.x, pp.y);
         }
-      }
+      };
+      if (masked) exp_pass(std::true_type{});
+      else exp_pass(std::false_type{});
       tmem_st32(tmem_base + lane_base + kColP + h * kHalfN, pk);
       tc_wait_st();
       tc_fence_before();

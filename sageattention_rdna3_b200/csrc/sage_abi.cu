@@ -103,10 +103,10 @@ int v_block_count(long long B, long long H, long long S, int D) {
   return static_cast<int>((n_vec + sage::kPrepThreads * 4 - 1) / (sage::kPrepThreads * 4));
 }
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool DUMP>
 int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const sage::AttnParams& p,
                 cudaStream_t stream) {
-  auto kern = sage::sage_attn_kernel<D, CAUSAL>;
+  auto kern = sage::sage_attn_kernel<D, CAUSAL, DUMP>;
   constexpr int kSmem = sage::AttnSmem<D>::kTotal;
   static bool configured[64] = {};
   int dev = 0;
@@ -231,6 +231,9 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
   p.q_groups = (Sq + sage::kQGroupRows - 1) / sage::kQGroupRows;
   p.k_groups = (Skv + sage::kKGroupRows - 1) / sage::kKGroupRows;
   p.n_q_tiles = (Sq + sage::kBlockM - 1) / sage::kBlockM;
+  // 8 heads at a time (each needs Skv * D * 3 bytes of K and V in L2), whole GQA groups only
+  const int rep = Hq / Hkv;
+  p.head_group = rep * ((8 + rep - 1) / rep);
   p.out_bf16 = (out_dtype == SAGE_DTYPE_BF16);
   p.s_dump = s_dump;
   p.status = status;
@@ -278,10 +281,12 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
     if (rc) return rc;
   }
 
-  if (D == 128) {
-    return is_causal ? launch_attn<128, true>(tq, tk, tv, p, st) : launch_attn<128, false>(tq, tk, tv, p, st);
-  }
-  return is_causal ? launch_attn<64, true>(tq, tk, tv, p, st) : launch_attn<64, false>(tq, tk, tv, p, st);
+  const bool dump = (s_dump != nullptr);
+#define SAGE_LAUNCH(DD, CC)                                                     \
+  (dump ? launch_attn<DD, CC, true>(tq, tk, tv, p, st) : launch_attn<DD, CC, false>(tq, tk, tv, p, st))
+  if (D == 128) return is_causal ? SAGE_LAUNCH(128, true) : SAGE_LAUNCH(128, false);
+  return is_causal ? SAGE_LAUNCH(64, true) : SAGE_LAUNCH(64, false);
+#undef SAGE_LAUNCH
 }
 
 }  // extern "C"
