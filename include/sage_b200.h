@@ -81,6 +81,34 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
                              const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv, int D,
                              int is_causal, int32_t* s_dump, int* status, void* stream);
 
+/* Smooth-K quantisation for callers that must not allocate device memory.
+ * No counterpart in the reference (its launchers allocate through torch).
+ *
+ * Who this is for: hosts in which a device allocation at call time is off limits - an inference
+ * engine that sized all of its memory when it started and treats a later cudaMalloc as a bug, a
+ * plugin whose host owns the only allocator and does not lend it out, a latency-critical loop that
+ * cannot take the driver lock and implicit device-wide synchronisation of cudaMalloc / cudaFree.
+ * sage_quant_qk_int8 with smooth_k needs one intermediate, the per-channel mean of K
+ * ([B,Hkv,D] in the input dtype); the other entry points leave it to the caller to allocate.  This
+ * one keeps it in a fixed buffer that is part of the library image, so the caller passes only the
+ * inputs (q, k) and the outputs (q_i8, q_scale, k_i8, k_scale), exactly as for
+ * sage_quant_qk_int8; the results are bit-identical to sage_mean_seq + sage_quant_qk_int8.
+ *
+ * Limit: B * Hkv * D <= SAGE_STATIC_KMEAN_MAX_ELEMS (65536 elements = 128 KB; every GPU on which
+ * the library is used holds that buffer until the process exits).  Larger problems are refused with
+ * SAGE_ERR_INVALID and a message; Skv must be >= 1.
+ * The function calls no cudaMalloc / cudaFree and no allocating library routine.  The first call
+ * on each device looks up the buffer's device address (cudaGetSymbolAddress); make that first call
+ * outside of any stream capture.
+ * The buffer is shared by all calls and keeps the last call's contents.  Nothing in it has to start
+ * at zero: the mean kernel overwrites every element the quantisation reads.  Two calls that may
+ * overlap on the GPU (different streams, or different host threads without ordering) race on it:
+ * order them with events or use the allocating entry points. */
+#define SAGE_STATIC_KMEAN_MAX_ELEMS 65536
+int sage_quant_qk_int8_smooth_static(const sage_strided_t* q, const sage_strided_t* k, int dtype, int B, int Hq,
+                                     int Hkv, int Sq, int Skv, int D, float sm_scale, int8_t* q_i8, float* q_scale,
+                                     int8_t* k_i8, float* k_scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,8 @@ def load_abi() -> ctypes.CDLL:
     lib.sage_mean_seq.argtypes = [sp, i, i, i, i, i, vp, vp]
     lib.sage_quant_qk_int8.restype = i
     lib.sage_quant_qk_int8.argtypes = [sp, sp, vp, sp, vp, i, i, i, i, i, i, i, f, vp, vp, vp, vp, vp]
+    lib.sage_quant_qk_int8_smooth_static.restype = i
+    lib.sage_quant_qk_int8_smooth_static.argtypes = [sp, sp, i, i, i, i, i, i, i, f, vp, vp, vp, vp, vp]
     lib.sage_v_to_f16.restype = i
     lib.sage_v_to_f16.argtypes = [sp, i, i, i, i, i, vp, vp]
     lib.sage_qk_int8_sv_f16_attn.restype = i

@@ -13,6 +13,10 @@
 #include "attn_kernel.cuh"
 #include "prep_kernels.cuh"
 
+// K-mean scratch of sage_quant_qk_int8_smooth_static: part of the library image, never allocated.
+// In host code this name is only a handle for cudaGetSymbolAddress, not a device address.
+static __device__ __align__(256) unsigned char g_static_kmean[SAGE_STATIC_KMEAN_MAX_ELEMS * 2];
+
 namespace {
 
 thread_local char g_err[512] = "";
@@ -122,6 +126,23 @@ int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   return SAGE_OK;
 }
 
+// Device address of g_static_kmean on the current device, looked up once per device.
+int static_kmean_address(void** out) {
+  static void* addr[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  SAGE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SAGE_ERR_INVALID, "device index %d is out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    SAGE_CUDA(cudaGetSymbolAddress(&p, g_static_kmean));
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return SAGE_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -187,6 +208,24 @@ int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const v
   p.k_blocks = static_cast<int>((kg + sage::kKGroupsPerBlock - 1) / sage::kKGroupsPerBlock);
   const int v_blocks = do_v ? v_block_count(B, Hkv, Skv, D) : 0;
   return dispatch_prep(dtype, D, p, v_blocks, static_cast<cudaStream_t>(stream));
+}
+
+int sage_quant_qk_int8_smooth_static(const sage_strided_t* q, const sage_strided_t* k, int dtype, int B, int Hq,
+                                     int Hkv, int Sq, int Skv, int D, float sm_scale, int8_t* q_i8, float* q_scale,
+                                     int8_t* k_i8, float* k_scale, void* stream) {
+  SAGE_REQUIRE(B > 0 && Hkv > 0 && D > 0 && Skv >= 1, "sage_quant_qk_int8_smooth_static: bad sizes (Skv must be >= 1)");
+  const long long elems = static_cast<long long>(B) * Hkv * D;
+  SAGE_REQUIRE(elems <= SAGE_STATIC_KMEAN_MAX_ELEMS,
+               "sage_quant_qk_int8_smooth_static: B*Hkv*D = %lld exceeds the built-in K-mean buffer of %d elements; "
+               "use sage_mean_seq + sage_quant_qk_int8 with a caller-allocated mean",
+               elems, SAGE_STATIC_KMEAN_MAX_ELEMS);
+  void* mean = nullptr;
+  int rc = static_kmean_address(&mean);
+  if (rc) return rc;
+  rc = sage_mean_seq(k, dtype, B, Hkv, Skv, D, mean, stream);
+  if (rc) return rc;
+  return sage_quant_qk_int8(q, k, mean, nullptr, nullptr, dtype, B, Hq, Hkv, Sq, Skv, D, sm_scale, q_i8, q_scale,
+                            k_i8, k_scale, stream);
 }
 
 int sage_v_to_f16(const sage_strided_t* v, int dtype, int B, int H, int S, int D, void* v16, void* stream) {
