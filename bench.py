@@ -147,6 +147,11 @@ def cpu_oracle_run(w, name, steps, warmup):
     """Times the CPU oracle on a bounded sample: one (batch, kv-head) unit of the workload with
     its full sequence length.  Returns (TOPS of the sample, description, threads)."""
     from oracle import sage_oracle as so
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every core this process may use
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     rep = w["Hq"] // w["Hkv"]
     S = w["S"]
     rows = S
@@ -161,6 +166,7 @@ def cpu_oracle_run(w, name, steps, warmup):
     ops = 4.0 * rep * rows * S * w["D"]
     sample = (f"1 of {w['B'] * w['Hkv']} (batch, kv-head) units of {name} ({rep} query head(s), S={S}, D={w['D']}), "
               f"median of {steps} run(s) after {warmup} warm-up")
+    cpu_oracle_run.last_ms = t * 1e3
     return ops / t / 1e12, sample, torch.get_num_threads()
 
 
@@ -172,7 +178,8 @@ def run_reference(args, w, name, rank):
     tops, sample, threads = cpu_oracle_run(w, name, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+        "steps": steps, "warmup": warmup, "ms_per_step": cpu_oracle_run.last_ms, "higher_is_better": True,
+        "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 x int8 -> int32 (QK^T), fp16 x fp16 -> fp32 (PV)", "data": "synthetic",
         "config": {"workload": workload_string(name, w)},
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},

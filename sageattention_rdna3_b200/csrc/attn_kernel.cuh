@@ -203,14 +203,25 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
 // A failed wait records which barrier it was and leaves the role's loop.
-#define SAGE_WAIT_OR(bar_ptr, parity, bar_id, action)              \
-  if (!mbar_wait((bar_ptr), (parity), abort_flag)) {               \
-    atomicCAS(fail_code, 0, kStatusWaitTimeout + 16 * (bar_id));   \
-    action;                                                        \
+#ifndef SAGE_HINT_TMA
+#define SAGE_HINT_TMA true
+#endif
+#ifndef SAGE_HINT_MMA
+#define SAGE_HINT_MMA true
+#endif
+#ifndef SAGE_HINT_SOFTMAX
+#define SAGE_HINT_SOFTMAX true
+#endif
+#define SAGE_WAIT_ROLE_OR(hinted, bar_ptr, parity, bar_id, action)   \
+  if (!mbar_wait<hinted>((bar_ptr), (parity), abort_flag)) {        \
+    atomicCAS(fail_code, 0, kStatusWaitTimeout + 16 * (bar_id));    \
+    action;                                                         \
   }
+#define SAGE_WAIT_OR(bar_ptr, parity, bar_id, action) SAGE_WAIT_ROLE_OR(kHintRole, bar_ptr, parity, bar_id, action)
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
+    constexpr bool kHintRole = SAGE_HINT_TMA;
     // Order of issue: Q, K(0), then for every tile K(j+1) before V(j): K is needed first.
     if (lane == 0 && n_kv > 0) {
       const int bhkv = b * p.Hkv + hkv;
@@ -240,6 +251,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncwarp();
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
+    constexpr bool kHintRole = SAGE_HINT_MMA;
     // Program order of the tensor pipe: QK(0,0) QK(0,1) | PV(0,0) QK(1,0) PV(0,1) QK(1,1) | ...
     // so the scores of the next half are ready while the softmax warps work on the current one.
     if (lane == 0 && n_kv > 0) {
@@ -305,6 +317,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
+    constexpr bool kHintRole = SAGE_HINT_SOFTMAX;
     const int row = q_base + threadIdx.x;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t t_o = tmem_base + lane_base + kColO;
@@ -473,6 +486,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   }
 #undef SAGE_WAIT_OR
+#undef SAGE_WAIT_ROLE_OR
 
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();

@@ -49,13 +49,18 @@ template <> __device__ __forceinline__ float elem_to_float<__nv_bfloat16>(__nv_b
   return __bfloat162float(v);
 }
 
-// csrc/attn_gfx11.cu:85-92: add +-0.5, convert toward zero, clamp to [-128, 127].
+// csrc/attn_gfx11.cu:85-92: add +-0.5 (sign of the value), convert toward zero, clamp to
+// [-128, 127].  Returned as int32 without the clamp; pack_s8x4 saturates.  copysign differs from
+// the reference's (x >= 0 ? .5 : -.5) only for -0.0 and NaN, which both give 0 either way.
 __device__ __forceinline__ int quantise_one(float y) {
-  y = __fadd_rn(y, (y >= 0.0f) ? 0.5f : -0.5f);
-  int r = __float2int_rz(y);
-  r = r > 127 ? 127 : r;
-  r = r < -128 ? -128 : r;
-  return r;
+  return __float2int_rz(__fadd_rn(y, copysignf(0.5f, y)));
+}
+// Four int32 -> four saturated int8 in one word, a in the lowest byte.
+__device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+  return out;
 }
 
 // One warp handles 16 consecutive rows (all D columns) of one (b,h): a K group, or half of a Q
@@ -66,7 +71,7 @@ constexpr int kRowsPerWarp = 16;
 constexpr int kQGroupsPerBlock = kPrepWarps / 2;
 constexpr int kKGroupsPerBlock = kPrepWarps;
 
-template <typename T, int D>
+template <typename T, int D, bool HAS_MEAN>
 struct RowSlab {
   static constexpr int kLanesPerRow = D / 8;
   static constexpr int kRowsPerPass = 32 / kLanesPerRow;
@@ -87,12 +92,18 @@ struct RowSlab {
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) mean8[i] = 0.0f;
-    if (mean_bh != nullptr) {
+    if (HAS_MEAN) {
       const uint4 mraw = __ldg(reinterpret_cast<const uint4*>(mean_bh + col));
       const T* mv = reinterpret_cast<const T*>(&mraw);
 #pragma unroll
       for (int i = 0; i < 8; ++i) mean8[i] = elem_to_float<T>(mv[i]);
     }
+  }
+
+  // x - mean in fp32 (csrc/attn_gfx11.cu:209-219); x itself when there is no mean
+  __device__ __forceinline__ float centred(T x, int i) const {
+    const float v = elem_to_float<T>(x);
+    return HAS_MEAN ? __fsub_rn(v, mean8[i]) : v;
   }
 
   // pass 1 (csrc/attn_gfx11.cu:189-237): abs-max of (x - mean) over the warp's rows
@@ -104,7 +115,7 @@ struct RowSlab {
       if (row < S) {
         const T* xv = reinterpret_cast<const T*>(&raw[p]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(__fsub_rn(elem_to_float<T>(xv[i]), mean8[i])));
+        for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(centred(xv[i], i)));
       }
     }
 #pragma unroll
@@ -119,14 +130,11 @@ struct RowSlab {
       const int row = row0 + p * kRowsPerPass + sub;
       if (row < S) {
         const T* xv = reinterpret_cast<const T*>(&raw[p]);
-        uint32_t packed[2] = {0u, 0u};
+        int qv[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float v = __fsub_rn(elem_to_float<T>(xv[i]), mean8[i]);
-          const int qv = quantise_one(__fmul_rn(v, iscale));
-          packed[i >> 2] |= (static_cast<uint32_t>(qv) & 0xFFu) << (8 * (i & 3));
-        }
-        *reinterpret_cast<uint2*>(out_bh + static_cast<long long>(row) * D + col) = make_uint2(packed[0], packed[1]);
+        for (int i = 0; i < 8; ++i) qv[i] = quantise_one(__fmul_rn(centred(xv[i], i), iscale));
+        *reinterpret_cast<uint2*>(out_bh + static_cast<long long>(row) * D + col) =
+            make_uint2(pack_s8x4(qv[0], qv[1], qv[2], qv[3]), pack_s8x4(qv[4], qv[5], qv[6], qv[7]));
       }
     }
   }
@@ -149,7 +157,7 @@ __global__ void __launch_bounds__(kPrepThreads, 3) sage_prep_kernel(const PrepPa
     const int row0 = grp * kQGroupRows + (warp & 1) * kRowsPerWarp;
     const int S = valid ? p.Sq : 0;
     const T* in_bh = reinterpret_cast<const T*>(p.q.ptr) + b * p.q.stride_b + h * p.q.stride_h;
-    RowSlab<T, D> slab;
+    RowSlab<T, D, false> slab;
     slab.load(in_bh, p.q.stride_s, row0, S, nullptr, lane);
     const float mine = slab.abs_max(row0, S);
     if (lane == 0) warp_max[warp] = mine;
@@ -174,13 +182,16 @@ __global__ void __launch_bounds__(kPrepThreads, 3) sage_prep_kernel(const PrepPa
     const T* in_bh = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h;
     const T* mean_bh =
         p.k_mean ? reinterpret_cast<const T*>(p.k_mean) + static_cast<long long>(bh) * D : nullptr;
-    RowSlab<T, D> slab;
-    slab.load(in_bh, p.k.stride_s, row0, p.Skv, mean_bh, lane);
-    const float vmax = slab.abs_max(row0, p.Skv);
-    const float amax = fmaxf(1e-7f, vmax);                               // s = 1 for K
-    if (lane == 0) p.k_scale[g] = __fdiv_rn(amax, 127.0f);
-    const float iscale = __fdiv_rn(127.0f, amax);
-    slab.quantise(row0, p.Skv, iscale, p.k_i8 + static_cast<long long>(bh) * p.Skv * D);
+    float* scale_out = p.k_scale + g;
+    int8_t* out_bh = p.k_i8 + static_cast<long long>(bh) * p.Skv * D;
+    auto run = [&](auto slab) {
+      slab.load(in_bh, p.k.stride_s, row0, p.Skv, mean_bh, lane);
+      const float amax = fmaxf(1e-7f, slab.abs_max(row0, p.Skv));        // s = 1 for K
+      if (lane == 0) *scale_out = __fdiv_rn(amax, 127.0f);
+      slab.quantise(row0, p.Skv, __fdiv_rn(127.0f, amax), out_bh);
+    };
+    if (mean_bh != nullptr) run(RowSlab<T, D, true>{});
+    else run(RowSlab<T, D, false>{});
     return;
   }
   blk -= p.k_blocks;

@@ -37,30 +37,45 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-// Upper bound, in nanoseconds, for how long one try_wait may keep the thread suspended; the thread
-// wakes as soon as the phase completes, so a long hint costs no latency and saves issue slots.
-constexpr uint32_t kTryWaitSuspendNs = 2000;
+// try_wait comes in two flavours.  The plain form returns after a short, hardware-defined time.
+// With a suspend-time hint the compiler emits a sleep loop: far fewer issue slots are spent on
+// waiting, but the wake-up can come late.  Which waits use which is chosen per role in the kernel.
+#ifndef SAGE_WAIT_HINT_NS
+#define SAGE_WAIT_HINT_NS 2000
+#endif
+template <bool kHinted>
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitSuspendNs)
-      : "memory");
+  if constexpr (kHinted) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(static_cast<uint32_t>(SAGE_WAIT_HINT_NS))
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  }
   return ok != 0;
 }
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the whole CTA.
+template <bool kHinted = true>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
-  for (int i = 0; i < 128; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  for (int i = 0; i < (kHinted ? 128 : 4096); ++i) {
+    if (mbar_try_wait<kHinted>(bar, parity)) return true;
   }
   const long long t0 = clock64();
 #pragma unroll 1
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait<kHinted>(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;
