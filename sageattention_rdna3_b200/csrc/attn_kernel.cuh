@@ -371,8 +371,52 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // columns below this bound are visible to this row (causal: col <= row; length: col < Skv)
       const int col_end = masked ? min(p.Skv, CAUSAL ? row + 1 : p.Skv) - kv_base : kHalfN;
 
+      // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs.  kTrack also
+      // returns max(s - m) so that the row maximum need not be known beforehand.
+      uint32_t pk[32];
+      auto exp_pass = [&](auto masked_tag, auto track_tag, float m_now, float2& l_acc) -> float {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+        constexpr bool kTrack = decltype(track_tag)::value;
+        const float2 neg_m = make_float2(-m_now, -m_now);
+        float xmax = kMaskValue;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int e = 32 * c + 2 * i;
+            const float cs = cg[e >> 4];
+            const float2 sf = make_float2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
+                                          __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
+            const float2 x = ffma2(sf, make_float2(cs, cs), neg_m);
+            if constexpr (kTrack) xmax = fmaxf(xmax, fmaxf(x.x, x.y));
+            float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            if constexpr (kMasked) {
+              if (e >= col_end) pp.x = 0.0f;
+              if (e + 1 >= col_end) pp.y = 0.0f;
+            }
+            l_acc = fadd2(l_acc, pp);
+            pk[16 * c + i] = pack_half2(pp.x, pp.y);
+          }
+        }
+        return xmax;
+      };
+
+      // Common case (not the first half, no mask): exponentiate against the running maximum
+      // straight away and only watch max(s - m).  As long as it stays below 2^8 the lazy-rescale
+      // rule would not have moved the maximum anyway, and the step is done without a separate
+      // pass over the scores.  Otherwise fall through to the exact path and redo the step.
+      bool done = false;
       float m_half = kMaskValue;
-      if (!masked) {
+      if (hh > 0 && !masked) {
+        float2 l_try = l2;
+        const float xmax = exp_pass(std::false_type{}, std::true_type{}, m_used, l_try);
+        if (!__any_sync(0xffffffffu, xmax > kLazyRescaleLog2)) {
+          l2 = l_try;
+          done = true;
+        } else {
+          m_half = m_used + xmax;
+        }
+      } else if (!masked) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {                   // scales are >= 0: max commutes with the scaling
           int mx = static_cast<int>(sr[g >> 1][(g & 1) * 16]);
@@ -390,60 +434,37 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
       }
 
-      // lazy rescale: move the running maximum only when it grew by more than 2^8
-      if (hh == 0) {
-        m_used = m_half;
-      } else {
-        const bool need = m_half > m_used + kLazyRescaleLog2;
-        if (__any_sync(0xffffffffu, need)) {
-          // O must be at rest: the P.V of the previous half has to be complete
-          const int hp = h ^ 1;
-          const int jp = (hh - 1) >> 1;
-          SAGE_WAIT_OR(pv_done + hp, jp & 1, 9, { ok = false; break; });
-          tc_fence_after();
-          const float alpha = need ? fast_exp2(m_used - m_half) : 1.0f;   // (:667)
-          if (need) m_used = m_half;
-          l2.x *= alpha;
-          l2.y *= alpha;
+      if (!done) {
+        // lazy rescale: move the running maximum only when it grew by more than 2^8
+        if (hh == 0) {
+          m_used = m_half;
+        } else {
+          const bool need = m_half > m_used + kLazyRescaleLog2;
+          if (__any_sync(0xffffffffu, need)) {
+            // O must be at rest: the P.V of the previous half has to be complete
+            const int hp = h ^ 1;
+            const int jp = (hh - 1) >> 1;
+            SAGE_WAIT_OR(pv_done + hp, jp & 1, 9, { ok = false; break; });
+            tc_fence_after();
+            const float alpha = need ? fast_exp2(m_used - m_half) : 1.0f;   // (:667)
+            if (need) m_used = m_half;
+            l2.x *= alpha;
+            l2.y *= alpha;
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t orr[32];
-            tmem_ld32(t_o + 32 * c, orr);
-            tc_wait_ld();
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld32(t_o + 32 * c, orr);
+              tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-            tmem_st32(t_o + 32 * c, orr);
-          }
-        }
-      }
-
-      // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs back into TMEM.
-      // Two copies of the loop: only tiles on the diagonal or at the ragged end pay for masking.
-      const float2 neg_m = make_float2(-m_used, -m_used);
-      uint32_t pk[32];
-      auto exp_pass = [&](auto masked_tag) {
-        constexpr bool kMasked = decltype(masked_tag)::value;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int e = 32 * c + 2 * i;
-            const float cs = cg[e >> 4];
-            const float2 sf = make_float2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
-                                          __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
-            const float2 x = ffma2(sf, make_float2(cs, cs), neg_m);
-            float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-            if constexpr (kMasked) {
-              if (e >= col_end) pp.x = 0.0f;
-              if (e + 1 >= col_end) pp.y = 0.0f;
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st32(t_o + 32 * c, orr);
             }
-            l2 = fadd2(l2, pp);
-            pk[16 * c + i] = pack_half2(pp.x, pp.y);
           }
         }
-      };
-      if (masked) exp_pass(std::true_type{});
-      else exp_pass(std::false_type{});
+        // Two copies of the loop: only tiles on the diagonal or at the ragged end pay for masking.
+        if (masked) exp_pass(std::true_type{}, std::false_type{}, m_used, l2);
+        else exp_pass(std::false_type{}, std::false_type{}, m_used, l2);
+      }
       tmem_st32(tmem_base + lane_base + kColP + h * kHalfN, pk);
       tc_wait_st();
       tc_fence_before();
