@@ -94,25 +94,28 @@ __device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
   return r;
 }
-// Packed fp32 pairs (sm_100): two fused multiply-adds / adds per instruction.
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+// Packed fp32 pairs (sm_100): two fused multiply-adds / adds per instruction.  A pair lives in a
+// 64-bit register; packing and unpacking are separate (and free when the halves are already
+// neighbouring registers), so constants are packed once and reused.
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack2(float lo, float hi) {
+  f32x2_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
   return d;
 }
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+__device__ __forceinline__ float2 unpack2(f32x2_t v) {
   float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "add.rn.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(v));
+  return d;
+}
+__device__ __forceinline__ f32x2_t ffma2(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2_t fadd2(f32x2_t a, f32x2_t b) {
+  f32x2_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
 
@@ -326,7 +329,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float* ks_base = p.k_scale + static_cast<long long>(b * p.Hkv + hkv) * p.k_groups;
 
     float m_used = kMaskValue;
-    float2 l2 = make_float2(0.0f, 0.0f);
+    f32x2_t l2 = pack2(0.0f, 0.0f);
     bool ok = true;
 
     // k_scale of the next half is fetched one half ahead, off the critical path
@@ -374,27 +377,29 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs.  kTrack also
       // returns max(s - m) so that the row maximum need not be known beforehand.
       uint32_t pk[32];
-      auto exp_pass = [&](auto masked_tag, auto track_tag, float m_now, float2& l_acc) -> float {
+      f32x2_t cg2[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) cg2[g] = pack2(cg[g], cg[g]);
+      auto exp_pass = [&](auto masked_tag, auto track_tag, float m_now, f32x2_t& l_acc) -> float {
         constexpr bool kMasked = decltype(masked_tag)::value;
         constexpr bool kTrack = decltype(track_tag)::value;
-        const float2 neg_m = make_float2(-m_now, -m_now);
+        const f32x2_t neg_m = pack2(-m_now, -m_now);
         float xmax = kMaskValue;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int e = 32 * c + 2 * i;
-            const float cs = cg[e >> 4];
-            const float2 sf = make_float2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
-                                          __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
-            const float2 x = ffma2(sf, make_float2(cs, cs), neg_m);
+            const f32x2_t sf = pack2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
+                                     __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
+            const float2 x = unpack2(ffma2(sf, cg2[e >> 4], neg_m));
             if constexpr (kTrack) xmax = fmaxf(xmax, fmaxf(x.x, x.y));
             float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
             if constexpr (kMasked) {
               if (e >= col_end) pp.x = 0.0f;
               if (e + 1 >= col_end) pp.y = 0.0f;
             }
-            l_acc = fadd2(l_acc, pp);
+            l_acc = fadd2(l_acc, pack2(pp.x, pp.y));
             pk[16 * c + i] = pack_half2(pp.x, pp.y);
           }
         }
@@ -408,7 +413,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bool done = false;
       float m_half = kMaskValue;
       if (hh > 0 && !masked) {
-        float2 l_try = l2;
+        f32x2_t l_try = l2;
         const float xmax = exp_pass(std::false_type{}, std::true_type{}, m_used, l_try);
         if (!__any_sync(0xffffffffu, xmax > kLazyRescaleLog2)) {
           l2 = l_try;
@@ -448,8 +453,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tc_fence_after();
             const float alpha = need ? fast_exp2(m_used - m_half) : 1.0f;   // (:667)
             if (need) m_used = m_half;
-            l2.x *= alpha;
-            l2.y *= alpha;
+            l2 = ffma2(l2, pack2(alpha, alpha), pack2(0.0f, 0.0f));
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t orr[32];
@@ -470,7 +474,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_before();
       mbar_arrive(p_full + h);
     }
-    const float l = l2.x + l2.y;
+    const float l = unpack2(l2).x + unpack2(l2).y;
 
     // ---- epilogue: o = acc * (1/l), one rounding to the output type (:769-786)
     if (ok && n_kv > 0) {
