@@ -94,31 +94,6 @@ __device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
   return r;
 }
-// Packed fp32 pairs (sm_100): two fused multiply-adds / adds per instruction.  A pair lives in a
-// 64-bit register; packing and unpacking are separate (and free when the halves are already
-// neighbouring registers), so constants are packed once and reused.
-typedef unsigned long long f32x2_t;
-__device__ __forceinline__ f32x2_t pack2(float lo, float hi) {
-  f32x2_t d;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
-  return d;
-}
-__device__ __forceinline__ float2 unpack2(f32x2_t v) {
-  float2 d;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(v));
-  return d;
-}
-__device__ __forceinline__ f32x2_t ffma2(f32x2_t a, f32x2_t b, f32x2_t c) {
-  f32x2_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ f32x2_t fadd2(f32x2_t a, f32x2_t b) {
-  f32x2_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-
 constexpr int kHalfN = kBlockN / 2;      // the softmax works on 64-column halves of a KV tile
 
 template <int D, bool CAUSAL, bool DUMP>

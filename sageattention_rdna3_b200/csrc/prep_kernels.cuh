@@ -17,6 +17,8 @@
 #include <cstdint>
 #include <type_traits>
 
+#include "ptx_sm100.cuh"
+
 namespace sage {
 
 struct StridedView {        // one of q / k / v in the caller's layout, strides in elements
@@ -71,51 +73,81 @@ constexpr int kRowsPerWarp = 16;
 constexpr int kQGroupsPerBlock = kPrepWarps / 2;
 constexpr int kKGroupsPerBlock = kPrepWarps;
 
+// Two 16-bit elements of one 32-bit word as fp32 (exact).
+template <typename T> __device__ __forceinline__ float2 word_to_float2(uint32_t w);
+template <> __device__ __forceinline__ float2 word_to_float2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+template <> __device__ __forceinline__ float2 word_to_float2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+// |x| of a 16-bit float from its magnitude bits (the bit pattern orders like the value).
+template <typename T> __device__ __forceinline__ float magnitude_to_float(uint32_t m16);
+template <> __device__ __forceinline__ float magnitude_to_float<__nv_bfloat16>(uint32_t m16) {
+  return __uint_as_float(m16 << 16);
+}
+template <> __device__ __forceinline__ float magnitude_to_float<__half>(uint32_t m16) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(m16)));
+}
+
 template <typename T, int D, bool HAS_MEAN>
 struct RowSlab {
   static constexpr int kLanesPerRow = D / 8;
   static constexpr int kRowsPerPass = 32 / kLanesPerRow;
   static constexpr int kPasses = kRowsPerWarp / kRowsPerPass;
   uint4 raw[kPasses];
-  float mean8[8];
+  f32x2_t neg_mean2[4];     // -mean of my 8 columns, as pairs: x - mean == x + (-mean) exactly
   int sub, col;
 
   __device__ __forceinline__ void load(const T* __restrict__ in_bh, long long stride_s, int row0, int S,
                                        const T* __restrict__ mean_bh, int lane) {
     sub = lane / kLanesPerRow;
     col = (lane % kLanesPerRow) * 8;
+    const T* src = in_bh + static_cast<long long>(row0 + sub) * stride_s + col;
+    const long long step = static_cast<long long>(kRowsPerPass) * stride_s;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
-      const int row = row0 + p * kRowsPerPass + sub;
       raw[p] = make_uint4(0u, 0u, 0u, 0u);
-      if (row < S) raw[p] = __ldg(reinterpret_cast<const uint4*>(in_bh + static_cast<long long>(row) * stride_s + col));
+      if (row0 + p * kRowsPerPass + sub < S) raw[p] = __ldg(reinterpret_cast<const uint4*>(src));
+      src += step;
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) mean8[i] = 0.0f;
     if (HAS_MEAN) {
       const uint4 mraw = __ldg(reinterpret_cast<const uint4*>(mean_bh + col));
-      const T* mv = reinterpret_cast<const T*>(&mraw);
+      const uint32_t* mw = reinterpret_cast<const uint32_t*>(&mraw);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mean8[i] = elem_to_float<T>(mv[i]);
+      for (int i = 0; i < 4; ++i) {
+        const float2 m = word_to_float2<T>(mw[i]);
+        neg_mean2[i] = pack2(-m.x, -m.y);
+      }
     }
   }
 
-  // x - mean in fp32 (csrc/attn_gfx11.cu:209-219); x itself when there is no mean
-  __device__ __forceinline__ float centred(T x, int i) const {
-    const float v = elem_to_float<T>(x);
-    return HAS_MEAN ? __fsub_rn(v, mean8[i]) : v;
-  }
-
-  // pass 1 (csrc/attn_gfx11.cu:189-237): abs-max of (x - mean) over the warp's rows
+  // pass 1 (csrc/attn_gfx11.cu:189-237): abs-max of (x - mean) over the warp's rows.  Without a
+  // mean the maximum is taken on the 15 magnitude bits, two elements per instruction; rows past
+  // the end were loaded as zeros and cannot win.
   __device__ __forceinline__ float abs_max(int row0, int S) const {
     float vmax = 0.0f;
+    if (!HAS_MEAN) {
+      uint32_t m2 = 0u;
 #pragma unroll
-    for (int p = 0; p < kPasses; ++p) {
-      const int row = row0 + p * kRowsPerPass + sub;
-      if (row < S) {
-        const T* xv = reinterpret_cast<const T*>(&raw[p]);
+      for (int p = 0; p < kPasses; ++p) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[p]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(centred(xv[i], i)));
+        for (int i = 0; i < 4; ++i) m2 = __vmaxu2(m2, w[i] & 0x7FFF7FFFu);
+      }
+      vmax = magnitude_to_float<T>(max(m2 & 0xFFFFu, m2 >> 16));
+    } else {
+#pragma unroll
+      for (int p = 0; p < kPasses; ++p) {
+        if (row0 + p * kRowsPerPass + sub < S) {
+          const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[p]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 x = word_to_float2<T>(w[i]);
+            const float2 v = unpack2(fadd2(pack2(x.x, x.y), neg_mean2[i]));
+            vmax = fmaxf(vmax, fmaxf(fabsf(v.x), fabsf(v.y)));
+          }
+        }
       }
     }
 #pragma unroll
@@ -123,25 +155,37 @@ struct RowSlab {
     return vmax;
   }
 
-  // pass 2 (csrc/attn_gfx11.cu:250-318): quantise from the registers, 8 bytes per lane and row
+  // pass 2 (csrc/attn_gfx11.cu:250-318): quantise from the registers, 8 bytes per lane and row.
+  // mul and add stay separate IEEE operations (packed two at a time), never an FMA.
   __device__ __forceinline__ void quantise(int row0, int S, float iscale, int8_t* __restrict__ out_bh) const {
+    const f32x2_t iscale2 = pack2(iscale, iscale);
+    int8_t* dst = out_bh + static_cast<long long>(row0 + sub) * D + col;
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
-      const int row = row0 + p * kRowsPerPass + sub;
-      if (row < S) {
-        const T* xv = reinterpret_cast<const T*>(&raw[p]);
+      if (row0 + p * kRowsPerPass + sub < S) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[p]);
         int qv[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qv[i] = quantise_one(__fmul_rn(centred(xv[i], i), iscale));
-        *reinterpret_cast<uint2*>(out_bh + static_cast<long long>(row) * D + col) =
+        for (int i = 0; i < 4; ++i) {
+          const float2 x = word_to_float2<T>(w[i]);
+          f32x2_t v2 = pack2(x.x, x.y);
+          if (HAS_MEAN) v2 = fadd2(v2, neg_mean2[i]);
+          const f32x2_t y2 = fmul2(v2, iscale2);
+          const float2 y = unpack2(y2);
+          const float2 z = unpack2(fadd2(y2, pack2(copysignf(0.5f, y.x), copysignf(0.5f, y.y))));
+          qv[2 * i] = __float2int_rz(z.x);
+          qv[2 * i + 1] = __float2int_rz(z.y);
+        }
+        *reinterpret_cast<uint2*>(dst) =
             make_uint2(pack_s8x4(qv[0], qv[1], qv[2], qv[3]), pack_s8x4(qv[4], qv[5], qv[6], qv[7]));
       }
+      dst += kRowsPerPass * D;
     }
   }
 };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kPrepThreads, 3) sage_prep_kernel(const PrepParams p) {
+__global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepParams p) {
   __shared__ float warp_max[kPrepWarps];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -230,41 +274,43 @@ __global__ void __launch_bounds__(kPrepThreads, 3) sage_prep_kernel(const PrepPa
 // K mean over the sequence, in the reference's summation order (csrc/attn_gfx11.cu:94-145):
 // 256 partial sums (thread t adds rows t, t+256, ... in fp32), then the 256 partials are added
 // serially from 0 to 255, then one fp32 division by float(S) and one rounding to the input type.
-// One CTA = one (b, h, 16-column slab); a thread reads 32 contiguous bytes of every row it owns.
+// One CTA = one (b, h, 32-column slab); a thread reads 64 contiguous bytes of every row it owns.
 struct MeanParams {
   StridedView k;
   void* mean_out;   // [B,H,D] in the input dtype
   int B, H, S, D;
 };
 
+constexpr int kMeanCols = 32;      // columns per CTA: a thread reads 64 contiguous bytes of each of its rows
+
 template <typename T>
 __global__ void __launch_bounds__(256) sage_kmean_kernel(const MeanParams p) {
-  constexpr int kCols = 16;
-  __shared__ float partial[kCols][257];
+  __shared__ float partial[kMeanCols][257];
   const int tid = threadIdx.x;
-  const int d0 = blockIdx.x * kCols;
+  const int d0 = blockIdx.x * kMeanCols;
   const int h = blockIdx.y, b = blockIdx.z;
   const T* base = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h + d0;
 
-  float acc[kCols];
+  float acc[kMeanCols];
 #pragma unroll
-  for (int c = 0; c < kCols; ++c) acc[c] = 0.0f;
-#pragma unroll 4
+  for (int c = 0; c < kMeanCols; ++c) acc[c] = 0.0f;
+#pragma unroll 2
   for (int s = tid; s < p.S; s += 256) {
     const uint4* src = reinterpret_cast<const uint4*>(base + static_cast<long long>(s) * p.k.stride_s);
-    const uint4 r0 = __ldg(src), r1 = __ldg(src + 1);
-    const T* v0 = reinterpret_cast<const T*>(&r0);
-    const T* v1 = reinterpret_cast<const T*>(&r1);
+    uint4 r[kMeanCols / 8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      acc[c] = __fadd_rn(acc[c], elem_to_float<T>(v0[c]));
-      acc[8 + c] = __fadd_rn(acc[8 + c], elem_to_float<T>(v1[c]));
+    for (int v = 0; v < kMeanCols / 8; ++v) r[v] = __ldg(src + v);
+#pragma unroll
+    for (int v = 0; v < kMeanCols / 8; ++v) {
+      const T* x = reinterpret_cast<const T*>(&r[v]);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[8 * v + c] = __fadd_rn(acc[8 * v + c], elem_to_float<T>(x[c]));
     }
   }
 #pragma unroll
-  for (int c = 0; c < kCols; ++c) partial[c][tid] = acc[c];
+  for (int c = 0; c < kMeanCols; ++c) partial[c][tid] = acc[c];
   __syncthreads();
-  if (tid < kCols) {
+  if (tid < kMeanCols) {
     float sum = 0.0f;
 #pragma unroll 8
     for (int i = 0; i < 256; ++i) sum = __fadd_rn(sum, partial[tid][i]);

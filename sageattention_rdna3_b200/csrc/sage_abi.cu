@@ -161,7 +161,7 @@ int sage_mean_seq(const sage_strided_t* k, int dtype, int B, int H, int S, int D
   p.k = view_of(k);
   p.mean_out = mean_out;
   p.B = B; p.H = H; p.S = S; p.D = D;
-  dim3 grid(D / 16, H, B);
+  dim3 grid(D / sage::kMeanCols, H, B);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == SAGE_DTYPE_F16) sage::sage_kmean_kernel<__half><<<grid, 256, 0, st>>>(p);
   else sage::sage_kmean_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
