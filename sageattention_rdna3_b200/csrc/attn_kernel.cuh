@@ -304,7 +304,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float* ks_base = p.k_scale + static_cast<long long>(b * p.Hkv + hkv) * p.k_groups;
 
     float m_used = kMaskValue;
-    f32x2_t l2 = pack2(0.0f, 0.0f);
+    float l = 0.0f;
     bool ok = true;
 
     // k_scale of the next half is fetched one half ahead, off the critical path
@@ -349,17 +349,16 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // columns below this bound are visible to this row (causal: col <= row; length: col < Skv)
       const int col_end = masked ? min(p.Skv, CAUSAL ? row + 1 : p.Skv) - kv_base : kHalfN;
 
-      // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs.  kTrack also
-      // returns max(s - m) so that the row maximum need not be known beforehand.
+      // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs.  Returns the sum of
+      // the 64 values of this half.
       uint32_t pk[32];
       f32x2_t cg2[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) cg2[g] = pack2(cg[g], cg[g]);
-      auto exp_pass = [&](auto masked_tag, auto track_tag, float m_now, f32x2_t& l_acc) -> float {
+      auto exp_pass = [&](auto masked_tag, float m_now) -> float {
         constexpr bool kMasked = decltype(masked_tag)::value;
-        constexpr bool kTrack = decltype(track_tag)::value;
         const f32x2_t neg_m = pack2(-m_now, -m_now);
-        float xmax = kMaskValue;
+        f32x2_t acc = pack2(0.0f, 0.0f);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
@@ -368,35 +367,35 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const f32x2_t sf = pack2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
                                      __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
             const float2 x = unpack2(ffma2(sf, cg2[e >> 4], neg_m));
-            if constexpr (kTrack) xmax = fmaxf(xmax, fmaxf(x.x, x.y));
             float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
             if constexpr (kMasked) {
               if (e >= col_end) pp.x = 0.0f;
               if (e + 1 >= col_end) pp.y = 0.0f;
             }
-            l_acc = fadd2(l_acc, pack2(pp.x, pp.y));
+            acc = fadd2(acc, pack2(pp.x, pp.y));
             pk[16 * c + i] = pack_half2(pp.x, pp.y);
           }
         }
-        return xmax;
+        const float2 a = unpack2(acc);
+        return a.x + a.y;
       };
 
       // Common case (not the first half, no mask): exponentiate against the running maximum
-      // straight away and only watch max(s - m).  As long as it stays below 2^8 the lazy-rescale
-      // rule would not have moved the maximum anyway, and the step is done without a separate
-      // pass over the scores.  Otherwise fall through to the exact path and redo the step.
+      // straight away.  If the 64 values add up to no more than 2^8, none of them exceeded 2^8:
+      // the lazy-rescale rule would not have moved the maximum, P fits fp16 comfortably, and the
+      // step is done without a pass over the scores for the maximum.  Otherwise (or if the sum is
+      // not a number) fall through to the exact path and redo the step.
       bool done = false;
       float m_half = kMaskValue;
-      if (hh > 0 && !masked) {
-        f32x2_t l_try = l2;
-        const float xmax = exp_pass(std::false_type{}, std::true_type{}, m_used, l_try);
-        if (!__any_sync(0xffffffffu, xmax > kLazyRescaleLog2)) {
-          l2 = l_try;
+      const bool first_or_masked = (hh == 0) || masked;
+      if (!first_or_masked) {
+        const float sum = exp_pass(std::false_type{}, m_used);
+        if (!__any_sync(0xffffffffu, !(sum <= 256.0f))) {
+          l += sum;
           done = true;
-        } else {
-          m_half = m_used + xmax;
         }
-      } else if (!masked) {
+      }
+      if (!done && !masked) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {                   // scales are >= 0: max commutes with the scaling
           int mx = static_cast<int>(sr[g >> 1][(g & 1) * 16]);
@@ -404,7 +403,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int i = 1; i < 16; ++i) mx = max(mx, static_cast<int>(sr[g >> 1][(g & 1) * 16 + i]));
           m_half = fmaxf(m_half, __int2float_rn(mx) * cg[g]);
         }
-      } else {
+      } else if (!done) {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -419,7 +418,9 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (hh == 0) {
           m_used = m_half;
         } else {
-          const bool need = m_half > m_used + kLazyRescaleLog2;
+          // After a refused attempt the bar is lower: a row whose 64 values added up to more
+          // than 2^8 has a maximum above 2^2, and it must move or it would be refused again.
+          const bool need = m_half > m_used + (first_or_masked ? kLazyRescaleLog2 : 1.5f);
           if (__any_sync(0xffffffffu, need)) {
             // O must be at rest: the P.V of the previous half has to be complete
             const int hp = h ^ 1;
@@ -428,7 +429,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tc_fence_after();
             const float alpha = need ? fast_exp2(m_used - m_half) : 1.0f;   // (:667)
             if (need) m_used = m_half;
-            l2 = ffma2(l2, pack2(alpha, alpha), pack2(0.0f, 0.0f));
+            l *= alpha;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t orr[32];
@@ -441,15 +442,14 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
         // Two copies of the loop: only tiles on the diagonal or at the ragged end pay for masking.
-        if (masked) exp_pass(std::true_type{}, std::false_type{}, m_used, l2);
-        else exp_pass(std::false_type{}, std::false_type{}, m_used, l2);
+        if (masked) l += exp_pass(std::true_type{}, m_used);
+        else l += exp_pass(std::false_type{}, m_used);
       }
       tmem_st32(tmem_base + lane_base + kColP + h * kHalfN, pk);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full + h);
     }
-    const float l = unpack2(l2).x + unpack2(l2).y;
 
     // ---- epilogue: o = acc * (1/l), one rounding to the output type (:769-786)
     if (ok && n_kv > 0) {
