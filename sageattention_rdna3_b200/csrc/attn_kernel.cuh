@@ -60,6 +60,8 @@ struct AttnParams {
   int out_bf16;
   int32_t* s_dump;              // optional [B,Hq,Sq,Skv] int32 copy of Q.K^T (debug / parity)
   int* status;                  // optional device word, stays 0 on success
+  long long wait_limit_cycles;  // bound of every barrier wait, in SM clocks
+  int test_drop_v_load;         // test hook: the producer never loads V of the first KV tile
 };
 
 template <int D>
@@ -191,7 +193,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #define SAGE_HINT_SOFTMAX true
 #endif
 #define SAGE_WAIT_ROLE_OR(hinted, bar_ptr, parity, bar_id, action)   \
-  if (!mbar_wait<hinted>((bar_ptr), (parity), abort_flag)) {        \
+  if (!mbar_wait<hinted>((bar_ptr), (parity), abort_flag, p.wait_limit_cycles)) { \
     atomicCAS(fail_code, 0, kStatusWaitTimeout + 16 * (bar_id));    \
     action;                                                         \
   }
@@ -219,6 +221,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int s = j % kStages;
         const uint32_t ph = (j / kStages) & 1;
         SAGE_WAIT_OR(v_empty + s, ph ^ 1u, 2, break);
+        if (p.test_drop_v_load && j == 0) continue;     // failure-detection test: v_full never completes
         mbar_arrive_expect_tx(v_full + s, L::kVBytes);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {

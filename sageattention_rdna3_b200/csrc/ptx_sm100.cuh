@@ -2,7 +2,8 @@
 // mbarrier, TMA tiled loads (cp.async.bulk.tensor), tcgen05 (alloc / mma / commit / ld / st / fence)
 // and the shared-memory / instruction descriptors of tcgen05.mma.
 //
-// Every wait in this file is bounded: it gives up after kWaitLimitCycles SM cycles (or as soon as
+// Every wait in this file is bounded: it gives up after a limit in SM cycles (kWaitLimitCycles unless
+// the caller passes another) or as soon as
 // another thread of the CTA has given up), raises the CTA-wide abort flag and returns false, so a
 // protocol error ends the kernel with a status code instead of hanging the GPU.
 #pragma once
@@ -67,7 +68,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the whole CTA.
 template <bool kHinted = true>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit_cycles = kWaitLimitCycles) {
 #pragma unroll 1
   for (int i = 0; i < (kHinted ? 128 : 4096); ++i) {
     if (mbar_try_wait<kHinted>(bar, parity)) return true;
@@ -77,7 +79,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   while (true) {
     if (mbar_try_wait<kHinted>(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
       return false;
     }

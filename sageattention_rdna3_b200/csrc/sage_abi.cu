@@ -7,6 +7,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -276,6 +277,15 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
   p.out_bf16 = (out_dtype == SAGE_DTYPE_BF16);
   p.s_dump = s_dump;
   p.status = status;
+  // Every barrier wait in the kernel gives up after this many SM clocks (about one second) and
+  // reports through `status`.  Two environment variables exist for the failure-detection test only:
+  // SAGE_WAIT_LIMIT_US shortens the bound, SAGE_TEST_DROP_V_LOAD makes a wait run out on purpose.
+  p.wait_limit_cycles = sage::kWaitLimitCycles;
+  if (const char* e = getenv("SAGE_WAIT_LIMIT_US")) {
+    const long long us = atoll(e);
+    if (us > 0) p.wait_limit_cycles = us * 2000;        // ~2 GHz
+  }
+  p.test_drop_v_load = (getenv("SAGE_TEST_DROP_V_LOAD") != nullptr) ? 1 : 0;
 
   // With no keys every row has l == 0 and the output is 0 (csrc/attn_gfx11.cu:771).  The kernel
   // handles that without touching K or V, but a tensor map cannot have a zero extent: describe one
