@@ -4,8 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C3] [--impl reference]
 
 One "step" is one pass of the hot path (K mean when smooth_k, Q/K quantisation + fp16 copy of V,
-fused attention) over one batch of synthetic input of the named workload.  The printed JSON line
-follows the driver's contract; see DESIGN.md ("Measurement") for what each key means here.
+fused attention) over one batch of synthetic input of the named workload.  One JSON line is printed:
 
 * ``value``     - attention TOPS, 4*B*Hq*Sq*Skv*D / t (benchmark_attn/benchmark_attn.py:40-47 of the
                   reference), inputs resident in HBM, aggregated over all ranks.
@@ -46,8 +45,8 @@ WORKLOADS = {
 }
 DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
 METRIC = "attention TOPS (4*B*H*S^2*D/t)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one sage_attn_kernel launch, from the ncu capture
-# summarised in profiles/sage_attn_kernel_C3.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one sage_attn_kernel launch, from an ncu capture of
+# this workload (ncu --set full -k regex:sage_ on `bench.py --steps 1 --warmup 3`)
 ATTN_TRAFFIC_BYTES = {"C3": 376.7e6}
 
 
