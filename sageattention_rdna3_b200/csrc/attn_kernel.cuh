@@ -309,6 +309,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     float m_used = kMaskValue;
     float l = 0.0f;
     bool ok = true;
+    bool refused_last = false;
 
     // k_scale of the next half is fetched one half ahead, off the critical path
     float ks_next[4];
@@ -391,13 +392,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bool done = false;
       float m_half = kMaskValue;
       const bool first_or_masked = (hh == 0) || masked;
-      if (!first_or_masked) {
+      // The attempt is skipped right after a refused one: data whose maxima keep jumping (heavy
+      // tails) would pay for two exp passes on most steps otherwise.
+      const bool attempt = !first_or_masked && !refused_last;
+      if (attempt) {
         const float sum = exp_pass(std::false_type{}, m_used);
         if (!__any_sync(0xffffffffu, !(sum <= 256.0f))) {
           l += sum;
           done = true;
         }
       }
+      refused_last = attempt && !done;
       if (!done && !masked) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {                   // scales are >= 0: max commutes with the scaling
@@ -423,7 +428,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         } else {
           // After a refused attempt the bar is lower: a row whose 64 values added up to more
           // than 2^8 has a maximum above 2^2, and it must move or it would be refused again.
-          const bool need = m_half > m_used + (first_or_masked ? kLazyRescaleLog2 : 1.5f);
+          const bool need = m_half > m_used + (attempt ? 1.5f : kLazyRescaleLog2);
           if (__any_sync(0xffffffffu, need)) {
             // O must be at rest: the P.V of the previous half has to be complete
             const int hp = h ^ 1;
