@@ -101,7 +101,8 @@ constexpr int kHalfN = kBlockN / 2;      // the softmax works on 64-column halve
 template <int D, bool CAUSAL, bool DUMP>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                 const AttnParams p) {
   using L = AttnSmem<D>;
   constexpr int kStages = L::kStages;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -153,6 +154,11 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *fail_code = 0;
+  }
+  if (warp == 4 && lane == 0) {
+    // The producer thread sets the barriers up itself and starts the first loads (Q and K tile 0,
+    // which wait for nothing) at once, so their latency overlaps the TMEM allocation and the
+    // CTA-wide barrier below.
     mbar_init(q_full, 1);
     mbar_init(o_final, 1);
     for (int h = 0; h < 2; ++h) {
@@ -167,11 +173,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(v_empty + s, 1);
     }
     fence_mbar_init();
-  }
-  if (warp == 4 && lane == 0) {
+    fence_proxy_async_smem();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_o);
+    if (n_kv > 0) {
+      mbar_arrive_expect_tx(q_full, L::kQBytes);
+      tma_load_3d(s_q, &tm_q, q_full, 0, q_base, bh);
+      mbar_arrive_expect_tx(k_full, L::kKBytes);
+      tma_load_3d(s_k, &tm_k, k_full, 0, 0, b * p.Hkv + hkv);
+    }
   }
   if (warp == 5) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -202,13 +214,9 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     constexpr bool kHintRole = SAGE_HINT_TMA;
-    // Order of issue: Q, K(0), then for every tile K(j+1) before V(j): K is needed first.
+    // Q and K(0) are already on their way; then for every tile K(j+1) before V(j): K is needed first.
     if (lane == 0 && n_kv > 0) {
       const int bhkv = b * p.Hkv + hkv;
-      mbar_arrive_expect_tx(q_full, L::kQBytes);
-      tma_load_3d(s_q, &tm_q, q_full, 0, q_base, bh);
-      mbar_arrive_expect_tx(k_full, L::kKBytes);
-      tma_load_3d(s_k, &tm_k, k_full, 0, 0, bhkv);
 #pragma unroll 1
       for (int j = 0; j < n_kv; ++j) {
         if (j + 1 < n_kv) {
@@ -465,9 +473,12 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_after();
     }
     if (ok) {
+      // Each warp stages its 32 rows in shared memory (the V ring is idle by now), one
+      // [32 rows][64 columns] box of 128-byte rows per 64 columns of head_dim, written with the
+      // 128-byte swizzle so that the 32 row owners do not collide on banks, and one lane hands the
+      // boxes to the TMA, which clips rows past Sq and follows the caller's strides.
       const float inv_l = (l > 0.0f) ? (1.0f / l) : 0.0f;
-      uint8_t* o_row = reinterpret_cast<uint8_t*>(p.o) +
-                       2 * (b * p.o_stride_b + hq * p.o_stride_h + static_cast<long long>(row) * p.o_stride_s);
+      uint8_t* stage = s_v + warp * ((D / 64) * 4096);
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t orr[32];
@@ -478,19 +489,30 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; ++i) orr[i] = 0u;
         }
-        if (row < p.Sq) {
-          uint32_t out[16];
+        uint32_t out[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float a = __uint_as_float(orr[2 * i]) * inv_l;
-            const float bb = __uint_as_float(orr[2 * i + 1]) * inv_l;
-            out[i] = p.out_bf16 ? pack_bf162(a, bb) : pack_half2(a, bb);
-          }
-          uint4* dst = reinterpret_cast<uint4*>(o_row + 64 * c);
+        for (int i = 0; i < 16; ++i) {
+          const float a = __uint_as_float(orr[2 * i]) * inv_l;
+          const float bb = __uint_as_float(orr[2 * i + 1]) * inv_l;
+          out[i] = p.out_bf16 ? pack_bf162(a, bb) : pack_half2(a, bb);
+        }
+        uint8_t* box = stage + (c >> 1) * 4096 + lane * 128;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+        for (int i = 0; i < 4; ++i) {
+          const int chunk = ((c & 1) * 4 + i) ^ (lane & 7);
+          *reinterpret_cast<uint4*>(box + chunk * 16) =
+              make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
         }
       }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && q_base + warp * 32 < p.Sq) {
+#pragma unroll
+        for (int bx = 0; bx < D / 64; ++bx) tma_store_4d(&tm_o, stage + bx * 4096, bx * 64, q_base + warp * 32, hq, b);
+        tma_store_commit();
+        tma_store_wait_read();
+      }
+      __syncwarp();
     }
   }
 #undef SAGE_WAIT_OR

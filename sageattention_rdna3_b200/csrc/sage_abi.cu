@@ -109,8 +109,8 @@ int v_block_count(long long B, long long H, long long S, int D) {
 }
 
 template <int D, bool CAUSAL, bool DUMP>
-int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const sage::AttnParams& p,
-                cudaStream_t stream) {
+int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+                const sage::AttnParams& p, cudaStream_t stream) {
   auto kern = sage::sage_attn_kernel<D, CAUSAL, DUMP>;
   constexpr int kSmem = sage::AttnSmem<D>::kTotal;
   static bool configured[64] = {};
@@ -122,7 +122,7 @@ int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   }
   const long long grid = static_cast<long long>(p.n_q_tiles) * p.B * p.Hq;
   if (grid > 0x7fffffffLL) return fail(SAGE_ERR_INVALID, "too many query tiles for one launch (%lld)", grid);
-  kern<<<static_cast<unsigned>(grid), sage::kAttnThreads, kSmem, stream>>>(tq, tk, tv, p);
+  kern<<<static_cast<unsigned>(grid), sage::kAttnThreads, kSmem, stream>>>(tq, tk, tv, to, p);
   SAGE_CUDA(cudaGetLastError());
   return SAGE_OK;
 }
@@ -294,7 +294,7 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
   const void* k_base = Skv > 0 ? static_cast<const void*>(k_i8) : static_cast<const void*>(q_i8);
   const void* v_base = Skv > 0 ? v16->ptr : static_cast<const void*>(q_i8);
 
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   const CUtensorMapSwizzle swz_qk = (D == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   {
     cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Sq, (cuuint64_t)B * Hq};
@@ -330,9 +330,28 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
     if (rc) return rc;
   }
 
+  {
+    // O in the caller's layout: (D, Sq, Hq, B) with the caller's strides; the kernel stores boxes of
+    // 32 rows x 64 columns.  Extent-1 dimensions get the span of the others, as for V.
+    cuuint64_t ss = (cuuint64_t)o_stride_s * 2, sh = (cuuint64_t)o_stride_h * 2, sb = (cuuint64_t)o_stride_b * 2;
+    cuuint64_t span = (cuuint64_t)D * 2;
+    if (Sq > 1 && ss * Sq > span) span = ss * Sq;
+    if (Hq > 1 && sh * Hq > span) span = sh * Hq;
+    if (B > 1 && sb * B > span) span = sb * B;
+    span = (span + 15) & ~(cuuint64_t)15;
+    if (Sq == 1) ss = span;
+    if (Hq == 1) sh = span;
+    if (B == 1) sb = span;
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)Sq, (cuuint64_t)Hq, (cuuint64_t)B};
+    cuuint64_t strides[3] = {ss, sh, sb};
+    cuuint32_t box[4] = {64, 32, 1, 1};
+    int rc = encode_map(&to, p.out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, o,
+                        dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "o");
+    if (rc) return rc;
+  }
   const bool dump = (s_dump != nullptr);
 #define SAGE_LAUNCH(DD, CC)                                                     \
-  (dump ? launch_attn<DD, CC, true>(tq, tk, tv, p, st) : launch_attn<DD, CC, false>(tq, tk, tv, p, st))
+  (dump ? launch_attn<DD, CC, true>(tq, tk, tv, to, p, st) : launch_attn<DD, CC, false>(tq, tk, tv, to, p, st))
   if (D == 128) return is_causal ? SAGE_LAUNCH(128, true) : SAGE_LAUNCH(128, false);
   return is_causal ? SAGE_LAUNCH(64, true) : SAGE_LAUNCH(64, false);
 #undef SAGE_LAUNCH
