@@ -8,9 +8,9 @@ fused attention) over one batch of synthetic input of the named workload.  One J
 
 * ``value``     - attention TOPS, 4*B*Hq*Sq*Skv*D / t (benchmark_attn/benchmark_attn.py:40-47 of the
                   reference), inputs resident in HBM, aggregated over all ranks.
-* ``e2e``       - the same metric through the public ``sageattn()`` call with HOST (pinned) q, k, v:
-                  the host->device copies and the device->host copy of the output are inside the
-                  timed region.
+* ``e2e``       - the same metric through the public ``sageattn_host()`` call with HOST (pinned) q, k,
+                  v and a host output: the host->device copies and the device->host copy of the
+                  output are inside the timed region (pipelined over streams by that call).
 * ``roofline``  - the fused attention kernel against the tensor-core roofline (executed flops).
 * ``cpu_baseline`` - the CPU oracle (a port of the reference's arithmetic) on the host cores, on a
                   bounded sample of the same workload.
@@ -230,7 +230,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    from sageattention_rdna3_b200 import _native, check_status, sageattn
+    from sageattention_rdna3_b200 import _native, check_status, sageattn_host
     from sageattention_rdna3_b200.shard import plan_shards
     ops = _native.load_ops()
 
@@ -315,11 +315,8 @@ def main():
             e2e_steps = max(3, min(args.steps, 20))
 
             def e2e_step():
-                qd = qp.to(dev, non_blocking=True)
-                kd = kp.to(dev, non_blocking=True)
-                vd = vp.to(dev, non_blocking=True)
-                od = sageattn(qd, kd, vd, tensor_layout=w["layout"], is_causal=w["causal"], smooth_k=w["smooth_k"])
-                o_host.copy_(od, non_blocking=True)
+                sageattn_host(qp, kp, vp, out=o_host, tensor_layout=w["layout"], is_causal=w["causal"],
+                              smooth_k=w["smooth_k"], device=dev)
 
             for _ in range(3):
                 e2e_step()

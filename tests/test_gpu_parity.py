@@ -335,3 +335,17 @@ def test_torch_ops_match_the_c_abi(dev):
     assert bits_equal(ops.v_to_f16(v, 1), b[4])
     with pytest.raises(RuntimeError, match="head_dim"):
         ops.quant_qk_int8(q[..., :96].contiguous(), k[..., :96].contiguous(), torch.empty(0, device=dev, dtype=q.dtype), 1, 0.1)
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+def test_host_pipeline_matches_device_call(dev, layout):
+    """sageattn_host (chunks over three streams) is bit-identical to one sageattn call."""
+    from sageattention_rdna3_b200 import check_status, sageattn, sageattn_host
+    B, Hq, Hkv, S, D = 2, 8, 4, 600, 128
+    shp = (lambda h: (B, h, S, D)) if layout == "HND" else (lambda h: (B, S, h, D))
+    q, k, v = (H.randn(shp(h), s, torch.bfloat16).pin_memory() for s, h in ((0, Hq), (1, Hkv), (2, Hkv)))
+    got = sageattn_host(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, device=dev, chunks=5)
+    torch.cuda.synchronize()
+    want = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=True, smooth_k=True).cpu()
+    check_status(dev)
+    assert torch.equal(got, want)
