@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SAGE_ABI_VERSION 1
+#define SAGE_ABI_VERSION 2
 
 #define SAGE_DTYPE_F16 0
 #define SAGE_DTYPE_BF16 1
@@ -80,6 +80,20 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
                              int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
                              const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv, int D,
                              int is_causal, int32_t* s_dump, int* status, void* stream);
+
+/* The same launch with the log-sum-exp of every query row written next to O.
+ * The reference accepts return_lse but returns zeros (sageattention/core.py:203-211, "LSE not
+ * computed by this kernel"); this entry point computes it, for callers that merge partial
+ * attention results (ring / context parallelism).
+ * lse (may be NULL: then this is sage_qk_int8_sv_f16_attn): [B,Hq,Sq] fp32, contiguous;
+ * lse[b,h,i] = ln sum_j exp(sm_scale * q_i . k_j) over the visible keys of row i, computed from
+ * the quantised scores (for K quantised with a mean subtracted it refers to the centred keys: add
+ * sm_scale * q_i . mean to obtain the value for the original keys); -inf for a row with no
+ * visible key. */
+int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                                 int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                                 const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                                 int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* stream);
 
 /* Smooth-K quantisation for callers that must not allocate device memory.
  * No counterpart in the reference (its launchers allocate through torch).

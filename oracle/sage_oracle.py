@@ -136,8 +136,10 @@ def qk_int32(q_i8: torch.Tensor, k_i8: torch.Tensor) -> torch.Tensor:
 
 def attention(q_i8: torch.Tensor, k_i8: torch.Tensor, v16_hnd: torch.Tensor,
               q_scale: torch.Tensor, k_scale: torch.Tensor, is_causal: bool,
-              out_dtype: torch.dtype, block_n: int = 64) -> torch.Tensor:
-    """Fused INT8 attention, blockwise online softmax in base 2.  Returns ``[B,Hq,Sq,D]``.
+              out_dtype: torch.dtype, block_n: int = 64, return_lse: bool = False):
+    """Fused INT8 attention, blockwise online softmax in base 2.  Returns ``[B,Hq,Sq,D]``
+    (and, with ``return_lse``, ``(m + log2 l) * ln 2`` per row, ``[B,Hq,Sq]`` fp32: the reference
+    keeps m and l (:499-500) but does not write them out, sageattention/core.py:203-211).
 
     csrc/attn_gfx11.cu:487-502 (state), :608-633 (scores, masks), :657-689 (softmax),
     :699-713 with csrc/mma_gfx11.h:97-106 (P rounded to fp16, fp32 accumulate), :769-786 (epilogue).
@@ -174,15 +176,21 @@ def attention(q_i8: torch.Tensor, k_i8: torch.Tensor, v16_hnd: torch.Tensor,
         p16 = p.to(torch.float16).to(torch.float32)                             # mma_gfx11.h:102-103
         acc = acc + torch.matmul(p16, vf[..., n0:n0 + block_n, :])              # :711
     inv_l = torch.where(l > 0, 1.0 / l, torch.zeros_like(l))                    # :771
-    return (acc * inv_l[..., None]).to(out_dtype)                               # :783-786
+    o = (acc * inv_l[..., None]).to(out_dtype)                                  # :783-786
+    if return_lse:
+        lse = torch.where(l > 0, (m + torch.log2(l)) * math.log(2.0), torch.full_like(l, float("-inf")))
+        return o, lse
+    return o
 
 
 def sageattn_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                       is_causal: bool = False, sm_scale: Optional[float] = None,
-                      smooth_k: bool = False, return_parts: bool = False):
+                      smooth_k: bool = False, return_parts: bool = False, return_lse: bool = False):
     """End-to-end emulation of ``sageattn``'s INT8 branch (sageattention/core.py:40-213).
 
-    fp32 inputs are computed in fp16 and returned in fp32 (core.py:78-83,200-201).
+    fp32 inputs are computed in fp16 and returned in fp32 (core.py:78-83,200-201).  With
+    ``return_lse`` the result is ``(o, lse)`` (or ``(o, lse, parts)``), lse ``[B,Hq,Sq]`` referring
+    to the caller's keys: ``sm_scale * q . mean`` is added back when the mean was subtracted.
     """
     in_dtype = q.dtype
     if in_dtype == torch.float32:
@@ -193,18 +201,23 @@ def sageattn_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_
     qh, kh, vh = to_hnd(q, tensor_layout), to_hnd(k, tensor_layout), to_hnd(v, tensor_layout)
     k_mean = mean_seq(kh) if smooth_k else None                                 # core.py:186-190
     q_i8, q_scale, k_i8, k_scale = quant_qk_int8(qh, kh, k_mean, sm_scale)
-    o = attention(q_i8, k_i8, v_to_f16(vh), q_scale, k_scale, is_causal, q.dtype)
+    o, lse = attention(q_i8, k_i8, v_to_f16(vh), q_scale, k_scale, is_causal, q.dtype, return_lse=True)
+    if smooth_k:
+        rep = qh.shape[1] // kh.shape[1]
+        km = k_mean.to(torch.float32).repeat_interleave(rep, dim=1)
+        lse = lse + torch.einsum("bhsd,bhd->bhs", qh.to(torch.float32), km) * sm_scale
     if tensor_layout == "NHD":
         o = o.permute(0, 2, 1, 3).contiguous()
     if in_dtype == torch.float32:
         o = o.to(torch.float32)
+    out = (o, lse) if return_lse else (o,)
     if return_parts:
-        return o, dict(q_i8=q_i8, q_scale=q_scale, k_i8=k_i8, k_scale=k_scale, k_mean=k_mean)
-    return o
+        out = out + (dict(q_i8=q_i8, q_scale=q_scale, k_i8=k_i8, k_scale=k_scale, k_mean=k_mean),)
+    return out if len(out) > 1 else out[0]
 
 
 def sdpa_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
-              is_causal: bool = False, sm_scale: Optional[float] = None) -> torch.Tensor:
+              is_causal: bool = False, sm_scale: Optional[float] = None, return_lse: bool = False):
     """The reference's own oracle: fp32 scaled-dot-product attention
     (test_sageattn_rdna3.py:20-24, benchmark_attn/benchmark_attn.py:50-66), with GQA heads
     repeated.  Causal masking is top-left aligned (``col > row``), as in the kernels.
@@ -223,6 +236,8 @@ def sdpa_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: 
     o = torch.matmul(torch.softmax(s, dim=-1), vh)
     if tensor_layout == "NHD":
         o = o.permute(0, 2, 1, 3).contiguous()
+    if return_lse:
+        return o, torch.logsumexp(s, dim=-1)                                    # [B,Hq,Sq]
     return o
 
 

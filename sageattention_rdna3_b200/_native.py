@@ -65,6 +65,9 @@ def load_abi() -> ctypes.CDLL:
     lib.sage_v_to_f16.argtypes = [sp, i, i, i, i, i, vp, vp]
     lib.sage_qk_int8_sv_f16_attn.restype = i
     lib.sage_qk_int8_sv_f16_attn.argtypes = [vp, vp, sp, vp, i64, i64, i64, vp, vp, i, i, i, i, i, i, i, i, vp, vp, vp]
+    lib.sage_qk_int8_sv_f16_attn_lse.restype = i
+    lib.sage_qk_int8_sv_f16_attn_lse.argtypes = [vp, vp, sp, vp, i64, i64, i64, vp, vp, i, i, i, i, i, i, i, i, vp, vp,
+                                                 vp, vp]
     _abi = lib
     return lib
 

@@ -67,8 +67,13 @@ def sageattn(
     (Hq a multiple of Hkv).  D in {64, 128}; fp16 / bf16, or fp32 which is computed in fp16 and
     returned in fp32 (``core.py:78-83,200-201``).  ``smooth_k`` subtracts the per-channel mean of K
     before quantisation (``core.py:186-190``; default False as in the native path).  Unknown keyword
-    arguments are ignored, as in the reference.  ``return_lse`` returns the reference's placeholder
-    zeros ``[B,Hq,Sq]`` (``core.py:203-211``).
+    arguments are ignored, as in the reference.
+
+    ``return_lse=True`` also returns ``lse`` ``[B,Hq,Sq]`` fp32, the natural-log sum of
+    ``exp(sm_scale * q.k)`` over the visible keys of each row, as computed by the kernel from the
+    quantised scores (with ``smooth_k`` the kernel works on centred keys and ``sm_scale * q.mean(k)``
+    is added back, so the value refers to the caller's keys).  The reference returns zeros there as
+    a placeholder (``core.py:203-211``); ``SAGEATTN_B200_LSE_ZEROS=1`` restores that.
     """
     dtype = q.dtype
     assert q.is_cuda, "Input tensors must be on CUDA/HIP device."
@@ -117,6 +122,14 @@ def sageattn(
         v = v.contiguous()
 
     o = torch.empty_like(q)
+    lse = None
+    want_lse = return_lse and os.environ.get("SAGEATTN_B200_LSE_ZEROS", "0") != "1"
+    if return_lse:
+        lse_shape = (q.size(0), q.size(head_dim_idx), q_len)
+        if want_lse:
+            lse = torch.full(lse_shape, float("-inf"), dtype=torch.float32, device=q.device)
+        else:
+            lse = torch.zeros(lse_shape, dtype=torch.float32, device=q.device)
     if q_len == 0 or q.size(0) == 0 or q.size(head_dim_idx) == 0:
         pass
     elif kv_len == 0:
@@ -136,7 +149,14 @@ def sageattn(
                 q_int8, q_scale, k_int8, k_scale = ops.quant_qk_int8(q, k, k_mean, layout, sm_scale)
                 v16, v_layout = v, layout
             ops.qk_int8_sv_f16_attn(q_int8, k_int8, v16, o, q_scale, k_scale, layout, v_layout,
-                                    int(is_causal), sm_scale, None, _status_word(q.device))
+                                    int(is_causal), sm_scale, None, _status_word(q.device),
+                                    lse if want_lse else None)
+            if want_lse and smooth_k:
+                # the kernel saw k - mean: every score of a row was lowered by sm_scale * q.mean
+                rep = q.size(head_dim_idx) // k.size(head_dim_idx)
+                km = k_mean.float().repeat_interleave(rep, dim=1)                   # [B,Hq,D]
+                eq = "bhsd,bhd->bhs" if tensor_layout == "HND" else "bshd,bhd->bhs"
+                lse += torch.einsum(eq, q.float(), km) * sm_scale
         if os.environ.get("SAGEATTN_B200_CHECK_STATUS", "0") == "1":
             check_status(q.device)
 
@@ -144,8 +164,6 @@ def sageattn(
         o = o.to(torch.float32)
 
     if return_lse:
-        # LSE is not computed by the reference kernel; it returns zeros as a placeholder
-        lse = torch.zeros((q.size(0), q.size(head_dim_idx), q_len), dtype=torch.float32, device=q.device)
         return o, lse
     return o
 

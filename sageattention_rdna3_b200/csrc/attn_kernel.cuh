@@ -59,6 +59,7 @@ struct AttnParams {
   int head_group;               // (batch, head) pairs scheduled together (a multiple of Hq/Hkv)
   int out_bf16;
   int32_t* s_dump;              // optional [B,Hq,Sq,Skv] int32 copy of Q.K^T (debug / parity)
+  float* lse;                   // optional [B,Hq,Sq]: natural-log sum of exp of the scaled scores
   int* status;                  // optional device word, stays 0 on success
   long long wait_limit_cycles;  // bound of every barrier wait, in SM clocks
   int test_drop_v_load;         // test hook: the producer never loads V of the first KV tile
@@ -478,6 +479,12 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // 128-byte swizzle so that the 32 row owners do not collide on banks, and one lane hands the
       // boxes to the TMA, which clips rows past Sq and follows the caller's strides.
       const float inv_l = (l > 0.0f) ? (1.0f / l) : 0.0f;
+      if (p.lse != nullptr && row < p.Sq) {
+        // scores are in base 2 (log2(e) is folded into the Q scale): ln sum exp = (m + log2 l) ln 2;
+        // a row without keys gets -inf
+        p.lse[static_cast<long long>(bh) * p.Sq + row] =
+            (l > 0.0f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
       uint8_t* stage = s_v + warp * ((D / 64) * 4096);
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {

@@ -272,50 +272,106 @@ __global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepPa
 
 // ---------------------------------------------------------------------------------------------
 // K mean over the sequence, in the reference's summation order (csrc/attn_gfx11.cu:94-145):
-// 256 partial sums (thread t adds rows t, t+256, ... in fp32), then the 256 partials are added
+// 256 partial sums (partial t adds rows t, t+256, ... in fp32), then the 256 partials are added
 // serially from 0 to 255, then one fp32 division by float(S) and one rounding to the input type.
-// One CTA = one (b, h, 32-column slab); a thread reads 64 contiguous bytes of every row it owns.
+//
+// One cluster of 8 CTAs = one (b, h).  CTA r of the cluster owns the partials [32r, 32r+32): it
+// reads, for every block of 256 rows, the 32 consecutive rows that feed them (whole rows, 16 bytes
+// per thread, so a warp reads 512 contiguous bytes of a dense K), and keeps their running sums in
+// registers.  The partials are then exchanged through distributed shared memory: CTA o of the
+// cluster receives all 256 partials of the D/8 columns [o*D/8, (o+1)*D/8) and D/8 of its threads
+// add them in order.  Eight CTAs per (b, h) put 8x more loads in flight than one CTA per column
+// slab did, with every DRAM line read once by one warp.
 struct MeanParams {
   StridedView k;
   void* mean_out;   // [B,H,D] in the input dtype
   int B, H, S, D;
 };
 
-constexpr int kMeanCols = 32;      // columns per CTA: a thread reads 64 contiguous bytes of each of its rows
+constexpr int kMeanCluster = 8;                  // CTAs per (b, h)
+constexpr int kMeanPartials = 256;               // csrc/attn_gfx11.cu:94-145: one partial per thread of its block
+constexpr int kMeanPartialsPerCta = kMeanPartials / kMeanCluster;
 
-template <typename T>
-__global__ void __launch_bounds__(256) sage_kmean_kernel(const MeanParams p) {
-  __shared__ float partial[kMeanCols][257];
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t map_to_cta(const void* smem_ptr, uint32_t cta_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_ptr))), "r"(cta_rank));
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <typename T, int D>
+__global__ void __cluster_dims__(kMeanCluster, 1, 1) __launch_bounds__(256) sage_kmean_kernel(const MeanParams p) {
+  constexpr int kLanesPerRow = D / 8;                       // 16-byte pieces of a row
+  constexpr int kRowsPerPass = 256 / kLanesPerRow;          // rows the CTA reads at once
+  constexpr int kSets = kMeanPartialsPerCta / kRowsPerPass; // partials per thread
+  constexpr int kOwnCols = D / kMeanCluster;                // columns this CTA sums in the end
+  static_assert(kSets >= 1 && kOwnCols % 8 == 0, "tile shape");
+  __shared__ __align__(16) float part[kMeanPartials][kOwnCols];
+
   const int tid = threadIdx.x;
-  const int d0 = blockIdx.x * kMeanCols;
+  const uint32_t rank = blockIdx.x;                         // cluster = the 8 CTAs of one blockIdx.(y,z)
   const int h = blockIdx.y, b = blockIdx.z;
-  const T* base = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h + d0;
+  const int rr = tid / kLanesPerRow, c = tid % kLanesPerRow;
+  const T* base = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h + c * 8;
 
-  float acc[kMeanCols];
+  cluster_arrive();     // matched by the wait before the first remote store: every CTA has started
+
+  float acc[kSets][8];
 #pragma unroll
-  for (int c = 0; c < kMeanCols; ++c) acc[c] = 0.0f;
-#pragma unroll 2
-  for (int s = tid; s < p.S; s += 256) {
-    const uint4* src = reinterpret_cast<const uint4*>(base + static_cast<long long>(s) * p.k.stride_s);
-    uint4 r[kMeanCols / 8];
+  for (int j = 0; j < kSets; ++j)
 #pragma unroll
-    for (int v = 0; v < kMeanCols / 8; ++v) r[v] = __ldg(src + v);
+    for (int e = 0; e < 8; ++e) acc[j][e] = 0.0f;
+
+  const int p0 = static_cast<int>(rank) * kMeanPartialsPerCta + rr;        // first partial of this thread
+  constexpr int kUnroll = 4;
+  for (int s0 = 0; s0 < p.S; s0 += kMeanPartials * kUnroll) {
+    uint4 r[kUnroll][kSets];
 #pragma unroll
-    for (int v = 0; v < kMeanCols / 8; ++v) {
-      const T* x = reinterpret_cast<const T*>(&r[v]);
+    for (int u = 0; u < kUnroll; ++u)
 #pragma unroll
-      for (int c = 0; c < 8; ++c) acc[8 * v + c] = __fadd_rn(acc[8 * v + c], elem_to_float<T>(x[c]));
-    }
+      for (int j = 0; j < kSets; ++j) {
+        const int srow = s0 + u * kMeanPartials + p0 + j * kRowsPerPass;
+        r[u][j] = make_uint4(0u, 0u, 0u, 0u);
+        if (srow < p.S) r[u][j] = __ldg(reinterpret_cast<const uint4*>(base + static_cast<long long>(srow) * p.k.stride_s));
+      }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+      for (int j = 0; j < kSets; ++j) {
+        const int srow = s0 + u * kMeanPartials + p0 + j * kRowsPerPass;
+        if (srow < p.S) {                                   // a missing row adds nothing (not +0.0)
+          const T* x = reinterpret_cast<const T*>(&r[u][j]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[j][e] = __fadd_rn(acc[j][e], elem_to_float<T>(x[e]));
+        }
+      }
   }
+
+  // hand the partials to the CTAs that own their columns
+  cluster_wait();
+  const uint32_t owner = static_cast<uint32_t>((c * 8) / kOwnCols);
+  const int col_in_owner = (c * 8) % kOwnCols;
 #pragma unroll
-  for (int c = 0; c < kMeanCols; ++c) partial[c][tid] = acc[c];
-  __syncthreads();
-  if (tid < kMeanCols) {
+  for (int j = 0; j < kSets; ++j) {
+    const int pidx = p0 + j * kRowsPerPass;
+    const uint32_t dst = map_to_cta(&part[pidx][col_in_owner], owner);
+    st_cluster_f32x4(dst, acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+    st_cluster_f32x4(dst + 16, acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+  }
+  cluster_arrive();
+  cluster_wait();       // all 256 partials of this CTA's columns have landed; nobody writes here again
+
+  if (tid < kOwnCols) {
     float sum = 0.0f;
-#pragma unroll 8
-    for (int i = 0; i < 256; ++i) sum = __fadd_rn(sum, partial[tid][i]);
+#pragma unroll 16
+    for (int i = 0; i < kMeanPartials; ++i) sum = __fadd_rn(sum, part[i][tid]);
     const float value = __fdiv_rn(sum, static_cast<float>(p.S));
-    T* out = reinterpret_cast<T*>(p.mean_out) + (static_cast<long long>(b) * p.H + h) * p.D + d0 + tid;
+    T* out = reinterpret_cast<T*>(p.mean_out) + (static_cast<long long>(b) * p.H + h) * D + rank * kOwnCols + tid;
     if constexpr (std::is_same<T, __half>::value) {
       *out = __float2half_rn(value);
     } else {

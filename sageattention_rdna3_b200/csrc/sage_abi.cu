@@ -162,10 +162,15 @@ int sage_mean_seq(const sage_strided_t* k, int dtype, int B, int H, int S, int D
   p.k = view_of(k);
   p.mean_out = mean_out;
   p.B = B; p.H = H; p.S = S; p.D = D;
-  dim3 grid(D / sage::kMeanCols, H, B);
+  dim3 grid(sage::kMeanCluster, H, B);                  // one cluster of 8 CTAs per (b, h)
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == SAGE_DTYPE_F16) sage::sage_kmean_kernel<__half><<<grid, 256, 0, st>>>(p);
-  else sage::sage_kmean_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  if (dtype == SAGE_DTYPE_F16) {
+    if (D == 128) sage::sage_kmean_kernel<__half, 128><<<grid, 256, 0, st>>>(p);
+    else sage::sage_kmean_kernel<__half, 64><<<grid, 256, 0, st>>>(p);
+  } else {
+    if (D == 128) sage::sage_kmean_kernel<__nv_bfloat16, 128><<<grid, 256, 0, st>>>(p);
+    else sage::sage_kmean_kernel<__nv_bfloat16, 64><<<grid, 256, 0, st>>>(p);
+  }
   SAGE_CUDA(cudaGetLastError());
   return SAGE_OK;
 }
@@ -248,6 +253,14 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
                              int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
                              const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv, int D,
                              int is_causal, int32_t* s_dump, int* status, void* stream) {
+  return sage_qk_int8_sv_f16_attn_lse(q_i8, k_i8, v16, o, o_stride_b, o_stride_h, o_stride_s, q_scale, k_scale,
+                                      out_dtype, B, Hq, Hkv, Sq, Skv, D, is_causal, nullptr, s_dump, status, stream);
+}
+
+int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                                 int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                                 const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                                 int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* stream) {
   SAGE_REQUIRE(q_i8 && v16 && o && q_scale, "sage_qk_int8_sv_f16_attn: null pointer");
   SAGE_REQUIRE(Skv == 0 || (k_i8 && v16->ptr && k_scale), "sage_qk_int8_sv_f16_attn: null pointer");
   SAGE_REQUIRE(out_dtype == SAGE_DTYPE_F16 || out_dtype == SAGE_DTYPE_BF16,
@@ -276,6 +289,7 @@ int sage_qk_int8_sv_f16_attn(const int8_t* q_i8, const int8_t* k_i8, const sage_
   p.head_group = rep * ((8 + rep - 1) / rep);
   p.out_bf16 = (out_dtype == SAGE_DTYPE_BF16);
   p.s_dump = s_dump;
+  p.lse = lse;
   p.status = status;
   // Every barrier wait in the kernel gives up after this many SM clocks (about one second) and
   // reports through `status`.  Two environment variables exist for the failure-detection test only:

@@ -150,14 +150,16 @@ at::Tensor v_to_f16(const at::Tensor& v, int64_t layout) {
 
 // qk_int8_sv_f16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor q_scale,
 //                     Tensor k_scale, int tensor_layout, int is_causal, float sm_scale,
-//                     Tensor? s_dump, Tensor? status) -> Tensor
+//                     Tensor? s_dump, Tensor? status, Tensor? lse) -> Tensor
 // Counterpart of qk_int8_sv_bf16_attn_t (csrc/pybind_gfx11.cpp:19-23): query/key are the int8
 // [B,H,S,D] tensors from quant_qk_int8; `value` is fp16 in `value_layout`; `output` is fp16/bf16 in
 // `tensor_layout`.  sm_scale is already folded into q_scale and is accepted for signature parity.
+// `lse` (optional, fp32 [B,Hq,Sq]) receives the natural-log sum of exponentials of every row.
 at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, const at::Tensor& v, at::Tensor& o,
                                const at::Tensor& q_scale, const at::Tensor& k_scale, int64_t layout,
                                int64_t value_layout, int64_t is_causal, double /*sm_scale*/,
-                               const c10::optional<at::Tensor>& s_dump, const c10::optional<at::Tensor>& status) {
+                               const c10::optional<at::Tensor>& s_dump, const c10::optional<at::Tensor>& status,
+                               const c10::optional<at::Tensor>& lse) {
   TORCH_CHECK(q_i8.is_cuda() && q_i8.scalar_type() == at::kChar && q_i8.is_contiguous() && q_i8.dim() == 4,
               "query must be a contiguous int8 CUDA tensor [B,Hq,Sq,D]");
   TORCH_CHECK(k_i8.scalar_type() == at::kChar && k_i8.is_contiguous() && k_i8.dim() == 4,
@@ -188,13 +190,20 @@ at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, c
     TORCH_CHECK(status->scalar_type() == at::kInt && status->numel() >= 1 && status->is_cuda(), "status must be an int32 CUDA tensor");
     status_ptr = status->data_ptr<int>();
   }
+  float* lse_ptr = nullptr;
+  if (lse.has_value()) {
+    TORCH_CHECK(lse->scalar_type() == at::kFloat && lse->is_contiguous() && lse->numel() == B * Hq * Sq && lse->is_cuda(),
+                "lse must be a contiguous fp32 CUDA tensor [B,Hq,Sq]");
+    lse_ptr = lse->data_ptr<float>();
+  }
   c10::cuda::CUDAGuard guard(q_i8.device());
   const sage_strided_t vs = strided_of(v, value_layout);
   const sage_strided_t os = strided_of(o, layout);
-  check_rc(sage_qk_int8_sv_f16_attn(q_i8.data_ptr<int8_t>(), k_i8.data_ptr<int8_t>(), &vs, o.data_ptr(), os.stride_b,
-                                    os.stride_h, os.stride_s, q_scale.data_ptr<float>(), k_scale.data_ptr<float>(),
-                                    dtype_code(o), (int)B, (int)Hq, (int)Hkv, (int)Sq, (int)Skv, (int)D,
-                                    (int)is_causal, dump_ptr, status_ptr, current_stream(q_i8)),
+  check_rc(sage_qk_int8_sv_f16_attn_lse(q_i8.data_ptr<int8_t>(), k_i8.data_ptr<int8_t>(), &vs, o.data_ptr(), os.stride_b,
+                                        os.stride_h, os.stride_s, q_scale.data_ptr<float>(),
+                                        k_scale.data_ptr<float>(), dtype_code(o), (int)B, (int)Hq, (int)Hkv, (int)Sq,
+                                        (int)Skv, (int)D, (int)is_causal, lse_ptr, dump_ptr, status_ptr,
+                                        current_stream(q_i8)),
            "qk_int8_sv_f16_attn");
   return o;
 }
@@ -204,7 +213,7 @@ at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, c
 TORCH_LIBRARY(sageattention, m) {
   m.def("qk_int8_sv_f16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor q_scale, "
         "Tensor k_scale, int tensor_layout, int value_layout, int is_causal, float sm_scale, "
-        "Tensor? s_dump=None, Tensor? status=None) -> Tensor");
+        "Tensor? s_dump=None, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("quant_qk_int8(Tensor query, Tensor key, Tensor key_mean, int tensor_layout, float sm_scale) -> Tensor[]");
   m.def("prep_qkv(Tensor query, Tensor key, Tensor value, Tensor key_mean, int tensor_layout, float sm_scale) "
         "-> Tensor[]");

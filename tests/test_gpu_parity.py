@@ -273,15 +273,18 @@ def test_config5_long_sequence_row_blocks(dev):
 
 
 # ----------------------------------------------------------------------------------------------
-def test_api_contract_details(dev):
+def test_api_contract_details(dev, monkeypatch):
     from sageattention_rdna3_b200 import sageattn, sageattn_qk_int8_pv_fp16_cuda
     q, k, v = (H.randn((1, 2, 200, 64), s, torch.float32).to(dev) for s in (0, 1, 2))
     o32 = sageattn(q, k, v)                                   # fp32 in -> fp16 compute -> fp32 out
     assert o32.dtype == torch.float32
     o16 = sageattn(q.half(), k.half(), v.half())
     assert torch.equal(o32, o16.float())
-    o, lse = sageattn(q.half(), k.half(), v.half(), return_lse=True)      # placeholder zeros
+    monkeypatch.setenv("SAGEATTN_B200_LSE_ZEROS", "1")                    # the reference's placeholder
+    o, lse = sageattn(q.half(), k.half(), v.half(), return_lse=True)
     assert lse.shape == (1, 2, 200) and lse.dtype == torch.float32 and not lse.any()
+    assert torch.equal(o, o16)
+    monkeypatch.delenv("SAGEATTN_B200_LSE_ZEROS")
     o_kw = sageattn_qk_int8_pv_fp16_cuda(q.half(), k.half(), v.half(), bm_sel=1, pv_accum_dtype="fp32", smooth_k=False)
     assert torch.equal(o_kw, o16)                             # unknown kwargs are ignored
     with pytest.raises(AssertionError, match="head_dim"):
@@ -349,3 +352,70 @@ def test_host_pipeline_matches_device_call(dev, layout):
     want = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=True, smooth_k=True).cpu()
     check_status(dev)
     assert torch.equal(got, want)
+
+
+# ----------------------------------------------------------------------------------------------
+# Log-sum-exp output (the reference returns zeros; here the kernel writes it).
+LSE_CASES = [
+    # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth_k, k_offset
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, False, 0.0),
+    (2, 4, 2, 300, 333, 128, torch.bfloat16, "NHD", False, True, 1.5),
+    (1, 4, 1, 777, 777, 128, torch.bfloat16, "HND", True, True, -2.0),
+    (1, 2, 2, 130, 2048, 64, torch.float16, "NHD", True, False, 0.0),
+]
+
+
+@pytest.mark.parametrize("case", LSE_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_lse_matches_oracle_and_fp32(dev, case):
+    from sageattention_rdna3_b200 import check_status, sageattn
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth, off = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k, v = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype, offset=off), H.randn(sk, 2, dtype)
+    o, lse = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=causal, smooth_k=smooth,
+                      return_lse=True)
+    check_status(dev)
+    o_plain = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=causal, smooth_k=smooth)
+    assert torch.equal(o, o_plain)                               # asking for lse does not change O
+    assert lse.shape == (B, Hq, Sq) and lse.dtype == torch.float32
+    o_emu, lse_emu = so.sageattn_emulated(q, k, v, tensor_layout=layout, is_causal=causal, smooth_k=smooth,
+                                          return_lse=True)
+    # same quantised scores, different summation order and ex2.approx / lg2: 1e-3 absolute
+    assert (lse.cpu() - lse_emu).abs().max().item() < 1e-3
+    _, lse_ref = so.sdpa_fp32(q, k, v, tensor_layout=layout, is_causal=causal, return_lse=True)
+    # against un-quantised fp32 scores: the int8 error of the scores, a few 1e-2
+    assert (lse.cpu() - lse_ref).abs().max().item() < 5e-2
+
+
+def test_lse_through_the_c_abi_and_merge_of_two_kv_halves(dev):
+    """lse is what lets partial results over disjoint key sets be merged:
+    o = (e^{l1} o1 + e^{l2} o2) / (e^{l1} + e^{l2}).  Two launches over the halves of K/V, merged
+    on the host, must reproduce the launch over the whole."""
+    import ctypes
+    lib = H._native.load_abi()
+    B, Hh, S, D = 1, 2, 512, 128
+    q, k, v = (H.randn((B, Hh, S, D), s, torch.float16).to(dev) for s in (0, 1, 2))
+    sm = D ** -0.5
+
+    def run(kk, vv):
+        q_i8, q_scale, k_i8, k_scale, _ = H.abi_quant(q, kk, None, "HND", sm)
+        o = torch.empty_like(q)
+        lse = torch.full((B, Hh, S), float("nan"), dtype=torch.float32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        os_, vs = H.strided(o, "HND"), H.strided(vv, "HND")
+        rc = lib.sage_qk_int8_sv_f16_attn_lse(q_i8.data_ptr(), k_i8.data_ptr(), ctypes.byref(vs), o.data_ptr(),
+                                              os_.stride_b, os_.stride_h, os_.stride_s, q_scale.data_ptr(),
+                                              k_scale.data_ptr(), 0, B, Hh, Hh, S, kk.size(2), D, 0,
+                                              lse.data_ptr(), None, status.data_ptr(), H._stream())
+        assert rc == 0, lib.sage_last_error()
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        return o.float(), lse
+
+    o_all, lse_all = run(k, v)
+    o1, l1 = run(k[:, :, :256].contiguous(), v[:, :, :256].contiguous())
+    o2, l2 = run(k[:, :, 256:].contiguous(), v[:, :, 256:].contiguous())
+    lm = torch.logaddexp(l1, l2)
+    merged = o1 * torch.exp(l1 - lm)[..., None] + o2 * torch.exp(l2 - lm)[..., None]
+    assert (lm - lse_all).abs().max().item() < 1e-3
+    acc = so.accuracy(merged, o_all)
+    assert acc["cos"] >= 0.99999 and acc["max_abs"] < 2e-3, acc

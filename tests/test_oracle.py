@@ -178,3 +178,17 @@ def test_oracle_matches_golden(name):
     o_gold = torch.from_numpy(gold["o_bits"]).view(o.dtype)
     acc = so.accuracy(o.float(), o_gold.float())
     assert acc["cos"] > 0.999999 and acc["rel_l1"] < 1e-3, acc
+
+
+def test_lse_of_the_emulation_against_fp32_logsumexp():
+    """(m + log2 l) ln 2 of the quantised path, with the smooth_k shift added back, is the fp32
+    log-sum-exp up to the int8 error of the scores."""
+    q, k, v = (randn((1, 2, 200, 64), s, torch.float16) for s in (0, 1, 2))
+    k = (k.float() + 1.5).half()
+    for causal in (False, True):
+        for smooth in (False, True):
+            o, lse = so.sageattn_emulated(q, k, v, is_causal=causal, smooth_k=smooth, return_lse=True)
+            o_ref, lse_ref = so.sdpa_fp32(q, k, v, is_causal=causal, return_lse=True)
+            assert lse.shape == (1, 2, 200)
+            assert (lse - lse_ref).abs().max().item() < 5e-2
+            assert torch.equal(o, so.sageattn_emulated(q, k, v, is_causal=causal, smooth_k=smooth))
