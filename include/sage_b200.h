@@ -95,6 +95,21 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
                                  const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
                                  int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* stream);
 
+/* Un-quantised attention for short sequences: O = softmax2(sm_scale*log2(e) * Q K^T) V with Q and K
+ * in fp16 or bf16 as the caller holds them.
+ * Replaces fp16_attn_gfx11_t / bf16_attn_gfx11_t (csrc/attn_gfx11.h:21-39; csrc/attn_gfx11.cu:2275-2472,
+ * kernel direct_attn_kernel_impl_t :1468-1846), the branch the reference's sageattn takes when the
+ * quantisation launches would cost more than INT8 saves (sageattention/core.py:113-163).  Same
+ * arithmetic as there: fp32 accumulation of the 16-bit products, scores scaled by
+ * sm_scale*1.4426950408889634 in fp32, causal / length mask, base-2 online softmax, P in fp16,
+ * V in fp16, fp32 accumulation, one rounding of acc/l.
+ * q, k: strided views, dtype `dtype` (SAGE_DTYPE_*); v16: fp16 in any strided layout (for bf16
+ * inputs run sage_v_to_f16 first, as the reference converts inside v_transpose); o: dtype `dtype`.
+ * lse, status: as for sage_qk_int8_sv_f16_attn_lse (both may be NULL). */
+int sage_direct_attn(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
+                     int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status, void* stream);
+
 /* Smooth-K quantisation for callers that must not allocate device memory.
  * No counterpart in the reference (its launchers allocate through torch).
  *

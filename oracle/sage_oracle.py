@@ -160,7 +160,15 @@ def attention(q_i8: torch.Tensor, k_i8: torch.Tensor, v16_hnd: torch.Tensor,
         col = torch.arange(Skv)[None, :]
         s = torch.where(col > row, torch.tensor(NEG_BIG), s)                    # :628-630
     vf = v16_hnd.to(torch.float16).to(torch.float32).repeat_interleave(rep, dim=1)
+    return _online_softmax_pv(s, vf, out_dtype, block_n, return_lse)
 
+
+def _online_softmax_pv(s: torch.Tensor, vf: torch.Tensor, out_dtype: torch.dtype, block_n: int, return_lse: bool):
+    """Blockwise base-2 online softmax of masked fp32 scores ``s`` ``[B,Hq,Sq,Skv]`` and P.V with P
+    rounded to fp16 (csrc/attn_gfx11.cu:499-500, :657-689, :699-713, :769-786; the un-quantised
+    kernel does the same at :1552-1553, :1689-1745, :1790-1793)."""
+    B, Hq, Sq, Skv = s.shape
+    D = vf.shape[-1]
     m = torch.full((B, Hq, Sq), NEG_BIG, dtype=torch.float32)                   # :499
     l = torch.zeros(B, Hq, Sq, dtype=torch.float32)                             # :500
     acc = torch.zeros(B, Hq, Sq, D, dtype=torch.float32)
@@ -181,6 +189,44 @@ def attention(q_i8: torch.Tensor, k_i8: torch.Tensor, v16_hnd: torch.Tensor,
         lse = torch.where(l > 0, (m + torch.log2(l)) * math.log(2.0), torch.full_like(l, float("-inf")))
         return o, lse
     return o
+
+
+def direct_attn_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
+                         is_causal: bool = False, sm_scale: Optional[float] = None, block_n: int = 64,
+                         return_lse: bool = False):
+    """The reference's un-quantised branch (sageattention/core.py:141-163: v_transpose with the
+    bf16 -> fp16 conversion, then fp16_attn_t / bf16_attn_t; kernel csrc/attn_gfx11.cu:1468-1846).
+
+    Scores are fp32-accumulated products of the fp16 / bf16 inputs (:1662-1671), multiplied by
+    ``fl32(sm_scale * log2e)`` in fp32 (:1679), masked with ``-FLT_MAX/2`` for ``col > row`` and
+    ``col >= kv_len`` (:1680-1683); the rest is the same online softmax and fp16 P.V.  fp32 inputs
+    are computed in fp16 (core.py:78-83).  The accumulation order of a dot product inside the matrix
+    unit is not defined, so this path is compared by tolerance only.
+    """
+    in_dtype = q.dtype
+    if in_dtype == torch.float32:
+        q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
+    D = q.shape[-1]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    qh, kh, vh = to_hnd(q, tensor_layout), to_hnd(k, tensor_layout), to_hnd(v, tensor_layout)
+    rep = qh.shape[1] // kh.shape[1]
+    Sq, Skv = qh.shape[2], kh.shape[2]
+    c = (torch.tensor(float(sm_scale), dtype=torch.float32) * torch.tensor(LOG2E_F32, dtype=torch.float32))
+    kf = kh.to(torch.float32).repeat_interleave(rep, dim=1)
+    s = torch.matmul(qh.to(torch.float32), kf.transpose(-1, -2)) * c
+    if is_causal:
+        row = torch.arange(Sq)[:, None]
+        col = torch.arange(Skv)[None, :]
+        s = torch.where(col > row, torch.tensor(NEG_BIG), s)
+    vf = v_to_f16(vh).to(torch.float32).repeat_interleave(rep, dim=1)
+    out = _online_softmax_pv(s, vf, q.dtype, block_n, return_lse)
+    o, lse = out if return_lse else (out, None)
+    if tensor_layout == "NHD":
+        o = o.permute(0, 2, 1, 3).contiguous()
+    if in_dtype == torch.float32:
+        o = o.to(torch.float32)
+    return (o, lse) if return_lse else o
 
 
 def sageattn_emulated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",

@@ -50,6 +50,47 @@ def _aligned(t: torch.Tensor) -> bool:
     return t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])
 
 
+# Largest kv length that goes to the un-quantised kernel, per case of the reference's dispatch
+# (sageattention/core.py:113-139); the same environment variables override them.  The values are the
+# reference's: on a B200 the un-quantised kernel is at least as fast as the INT8 path everywhere
+# below them (head_dim 64: faster at every length measured, the exponential unit and not the tensor
+# pipe limits both kernels there; head_dim 128: level at kv = 2048, INT8 ahead by 1.2x at 8192), so
+# every call takes the branch the reference takes for its shape.
+_DIRECT_DEFAULTS = {
+    "SAGEATTN_DIRECT_THRESHOLD_D64": {"HND": 2048, "NHD": 3072},
+    "SAGEATTN_DIRECT_THRESHOLD_D64_CAUSAL": 6144,
+    "SAGEATTN_DIRECT_THRESHOLD_D64_CROSS": 6144,
+    "SAGEATTN_DIRECT_THRESHOLD_D128": 2048,
+    "SAGEATTN_DIRECT_THRESHOLD_D128_CROSS": 4096,
+}
+
+
+def _threshold(name: str, tensor_layout: str = "HND") -> int:
+    default = _DIRECT_DEFAULTS[name]
+    if isinstance(default, dict):
+        default = default[tensor_layout]
+    return int(os.environ.get(name, str(default)) or default)
+
+
+def use_direct_kernel(headdim: int, tensor_layout: str, is_causal: bool, q_len: int, kv_len: int) -> bool:
+    """The reference's choice between the un-quantised and the INT8 kernels
+    (``sageattention/core.py:113-139``): by head_dim, causal / cross / self attention and kv length.
+    ``SAGEATTN_KERNEL=int8`` or ``=direct`` in the environment overrides it for every call."""
+    forced = os.environ.get("SAGEATTN_KERNEL", "")
+    if forced:
+        assert forced in ("int8", "direct"), f"SAGEATTN_KERNEL must be 'int8' or 'direct', got {forced!r}."
+        return forced == "direct"
+    if headdim == 64:
+        if is_causal:
+            return kv_len <= _threshold("SAGEATTN_DIRECT_THRESHOLD_D64_CAUSAL")
+        if q_len < kv_len:
+            return kv_len <= _threshold("SAGEATTN_DIRECT_THRESHOLD_D64_CROSS")
+        return kv_len <= _threshold("SAGEATTN_DIRECT_THRESHOLD_D64", tensor_layout)
+    if q_len * 2 < kv_len:
+        return kv_len <= _threshold("SAGEATTN_DIRECT_THRESHOLD_D128_CROSS")
+    return kv_len <= _threshold("SAGEATTN_DIRECT_THRESHOLD_D128")
+
+
 def sageattn(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -68,6 +109,12 @@ def sageattn(
     returned in fp32 (``core.py:78-83,200-201``).  ``smooth_k`` subtracts the per-channel mean of K
     before quantisation (``core.py:186-190``; default False as in the native path).  Unknown keyword
     arguments are ignored, as in the reference.
+
+    Short sequences go to the un-quantised kernel (fp16 / bf16 Q.K^T, no quantisation launches), as
+    in the reference (``core.py:113-163``), below the kv lengths of ``_DIRECT_DEFAULTS``;
+    ``kernel="int8"`` or ``kernel="direct"`` (keyword, or ``SAGEATTN_KERNEL`` in the environment)
+    forces one of the two.  ``smooth_k`` only
+    applies to the INT8 kernel, as in the reference.
 
     ``return_lse=True`` also returns ``lse`` ``[B,Hq,Sq]`` fp32, the natural-log sum of
     ``exp(sm_scale * q.k)`` over the visible keys of each row, as computed by the kernel from the
@@ -134,6 +181,19 @@ def sageattn(
         pass
     elif kv_len == 0:
         o.zero_()                        # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
+    elif _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len):
+        with torch.cuda.device(q.device):
+            # core.py:141-163: V as fp16 (converted for bf16 inputs), then fp16_attn / bf16_attn
+            if dtype == torch.bfloat16:
+                v16, v_layout = ops.v_to_f16(v, layout), _LAYOUT_CODE["HND"]
+                op = ops.bf16_attn
+            else:
+                v16, v_layout = v, layout
+                op = ops.fp16_attn
+            op(q, k, v16, o, layout, v_layout, int(is_causal), sm_scale, 0, _status_word(q.device),
+               lse if want_lse else None)
+        if os.environ.get("SAGEATTN_B200_CHECK_STATUS", "0") == "1":
+            check_status(q.device)
     else:
         with torch.cuda.device(q.device):
             if smooth_k:
@@ -166,6 +226,14 @@ def sageattn(
     if return_lse:
         return o, lse
     return o
+
+
+def _pick_direct(forced: Optional[str], headdim: int, tensor_layout: str, is_causal: bool, q_len: int,
+                 kv_len: int) -> bool:
+    if forced is not None:
+        assert forced in ("int8", "direct"), f"kernel must be 'int8' or 'direct', got {forced!r}."
+        return forced == "direct"
+    return use_direct_kernel(headdim, tensor_layout, is_causal, q_len, kv_len)
 
 
 def sageattn_qk_int8_pv_fp16_cuda(

@@ -58,6 +58,8 @@ struct AttnParams {
   int n_q_tiles;
   int head_group;               // (batch, head) pairs scheduled together (a multiple of Hq/Hkv)
   int out_bf16;
+  int qk_bf16;                  // un-quantised variant only: Q and K are bf16 (else fp16)
+  float score_scale;            // un-quantised variant only: sm_scale * log2(e)
   int32_t* s_dump;              // optional [B,Hq,Sq,Skv] int32 copy of Q.K^T (debug / parity)
   float* lse;                   // optional [B,Hq,Sq]: natural-log sum of exp of the scaled scores
   int* status;                  // optional device word, stays 0 on success
@@ -65,11 +67,17 @@ struct AttnParams {
   int test_drop_v_load;         // test hook: the producer never loads V of the first KV tile
 };
 
-template <int D>
+// QKB = bytes per element of Q and K in shared memory: 1 (int8) or 2 (fp16 / bf16, the
+// un-quantised variant).
+// KST = depth of the K and V rings, 0 for the default.  16-bit Q/K with head_dim 128 has two
+// shapes: one K and one V tile (32 KB each) next to Q (32 KB) keep two CTAs on an SM - the
+// half-tile order of the tensor pipe still leaves each refill about one softmax half-step of lead
+// time - and two tiles each (160 KB, one CTA per SM) for grids that do not fill the SMs twice.
+template <int D, int QKB = 1, int KST = 0>
 struct AttnSmem {
-  static constexpr int kStages = (D == 128) ? 2 : 4;
-  static constexpr int kQBytes = kBlockM * D;            // int8
-  static constexpr int kKBytes = kBlockN * D;            // int8
+  static constexpr int kStages = KST > 0 ? KST : (QKB == 2) ? (D == 128 ? 1 : 2) : (D == 128 ? 2 : 4);
+  static constexpr int kQBytes = kBlockM * D * QKB;
+  static constexpr int kKBytes = kBlockN * D * QKB;
   static constexpr int kVBytes = kBlockN * D * 2;        // fp16
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + kQBytes;
@@ -99,13 +107,18 @@ __device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
 }
 constexpr int kHalfN = kBlockN / 2;      // the softmax works on 64-column halves of a KV tile
 
-template <int D, bool CAUSAL, bool DUMP>
+// QKF = false: Q and K are the int8 tensors of the quantised path (scores = int32 products times
+// q_scale*k_scale).  QKF = true: Q and K are the caller's fp16 / bf16 tensors, the scores are fp32
+// products times sm_scale*log2(e) - the reference's un-quantised kernels for short sequences
+// (direct_attn_kernel_impl_t, csrc/attn_gfx11.cu:1468-1846) on the same pipeline.
+template <int D, bool CAUSAL, bool DUMP, bool QKF = false, int KST = 0>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                  const AttnParams p) {
-  using L = AttnSmem<D>;
+  using L = AttnSmem<D, QKF ? 2 : 1, KST>;
   constexpr int kStages = L::kStages;
+  static_assert(!(QKF && DUMP), "the int32 score dump belongs to the quantised variant");
   extern __shared__ __align__(1024) uint8_t smem[];
 
   const int warp = threadIdx.x >> 5;
@@ -181,9 +194,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tma_prefetch_desc(&tm_o);
     if (n_kv > 0) {
       mbar_arrive_expect_tx(q_full, L::kQBytes);
-      tma_load_3d(s_q, &tm_q, q_full, 0, q_base, bh);
       mbar_arrive_expect_tx(k_full, L::kKBytes);
-      tma_load_3d(s_k, &tm_k, k_full, 0, 0, b * p.Hkv + hkv);
+      if constexpr (QKF) {
+        // 16-bit Q / K in the caller's layout: one [128 rows][64 columns] box per 64 columns
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_4d(s_q + c * (kBlockM * 128), &tm_q, q_full, c * 64, q_base, hq, b);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_4d(s_k + c * (kBlockN * 128), &tm_k, k_full, c * 64, 0, hkv, b);
+      } else {
+        tma_load_3d(s_q, &tm_q, q_full, 0, q_base, bh);
+        tma_load_3d(s_k, &tm_k, k_full, 0, 0, b * p.Hkv + hkv);
+      }
     }
   }
   if (warp == 5) {
@@ -225,7 +246,14 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint32_t ph1 = ((j + 1) / kStages) & 1;
           SAGE_WAIT_OR(k_empty + s1, ph1 ^ 1u, 1, break);
           mbar_arrive_expect_tx(k_full + s1, L::kKBytes);
-          tma_load_3d(s_k + s1 * L::kKBytes, &tm_k, k_full + s1, 0, (j + 1) * kBlockN, bhkv);
+          if constexpr (QKF) {
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_4d(s_k + s1 * L::kKBytes + c * (kBlockN * 128), &tm_k, k_full + s1, c * 64, (j + 1) * kBlockN,
+                          hkv, b);
+          } else {
+            tma_load_3d(s_k + s1 * L::kKBytes, &tm_k, k_full + s1, 0, (j + 1) * kBlockN, bhkv);
+          }
         }
         const int s = j % kStages;
         const uint32_t ph = (j / kStages) & 1;
@@ -253,13 +281,30 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint64_t desc_q = umma_smem_desc(smem_u32(s_q), 16, kSboQK, kSwzQK);
       const uint32_t t_o = tmem_base + kColO;
       bool ok = true;
+      // un-quantised variant: f32 = f16 x f16 or bf16 x bf16, both operands K-major
+      const uint32_t idesc_qk16 = umma_idesc(1, p.qk_bf16 ? 1u : 0u, p.qk_bf16 ? 1u : 0u, 0, 0, kBlockM, kHalfN);
 
       auto issue_qk = [&](int stage, int h) {
-        const uint64_t desc_k =
-            umma_smem_desc(smem_u32(s_k + stage * L::kKBytes + h * kHalfKBytes), 16, kSboQK, kSwzQK);
+        if constexpr (QKF) {
+          // Q and K tiles are D/64 slabs of [128 rows][64 elements = 128 bytes], 128-byte swizzle
+          // (8 rows = 1024 bytes); an instruction takes 16 elements = 32 bytes of head_dim, half h of
+          // K starts 64 rows = 8192 bytes into each slab.
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) {             // 32 int8 of head_dim per instruction
-          mma_i8_ss(tmem_base + kColS + h * kHalfN, desc_q + 2 * k, desc_k + 2 * k, kIdescQK, k > 0 ? 1u : 0u);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t slab = (k / 4) * (kBlockM * 128);
+            const uint64_t dq = umma_smem_desc(smem_u32(s_q + slab), 16, 1024, kSwizzle128B) + 2 * (k % 4);
+            const uint64_t dk =
+                umma_smem_desc(smem_u32(s_k + stage * L::kKBytes + slab + h * (kHalfN * 128)), 16, 1024, kSwizzle128B) +
+                2 * (k % 4);
+            mma_f16_ss(tmem_base + kColS + h * kHalfN, dq, dk, idesc_qk16, k > 0 ? 1u : 0u);
+          }
+        } else {
+          const uint64_t desc_k =
+              umma_smem_desc(smem_u32(s_k + stage * L::kKBytes + h * kHalfKBytes), 16, kSboQK, kSwzQK);
+#pragma unroll
+          for (int k = 0; k < D / 32; ++k) {           // 32 int8 of head_dim per instruction
+            mma_i8_ss(tmem_base + kColS + h * kHalfN, desc_q + 2 * k, desc_k + 2 * k, kIdescQK, k > 0 ? 1u : 0u);
+          }
         }
         tc_commit(s_full + h);
       };
@@ -312,8 +357,12 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t t_o = tmem_base + lane_base + kColO;
     const int q_grp = (q_base + warp * 32) / 32;
-    const float qs = (q_grp < p.q_groups) ? __ldg(p.q_scale + static_cast<long long>(bh) * p.q_groups + q_grp) : 0.0f;
-    const float* ks_base = p.k_scale + static_cast<long long>(b * p.Hkv + hkv) * p.k_groups;
+    float qs = 0.0f;
+    const float* ks_base = nullptr;
+    if constexpr (!QKF) {
+      qs = (q_grp < p.q_groups) ? __ldg(p.q_scale + static_cast<long long>(bh) * p.q_groups + q_grp) : 0.0f;
+      ks_base = p.k_scale + static_cast<long long>(b * p.Hkv + hkv) * p.k_groups;
+    }
 
     float m_used = kMaskValue;
     float l = 0.0f;
@@ -323,7 +372,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // k_scale of the next half is fetched one half ahead, off the critical path
     float ks_next[4];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) ks_next[g] = (g < p.k_groups) ? __ldg(ks_base + g) : 0.0f;
+    for (int g = 0; g < 4; ++g) ks_next[g] = (!QKF && g < p.k_groups) ? __ldg(ks_base + g) : 0.0f;
 
     const int n_half = 2 * n_kv;
 #pragma unroll 1
@@ -335,17 +384,19 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
       float cg[4];                                      // q_scale * k_scale per 16 columns (:621)
 #pragma unroll
-      for (int g = 0; g < 4; ++g) cg[g] = __fmul_rn(qs, ks_next[g]);
+      for (int g = 0; g < 4; ++g) cg[g] = QKF ? p.score_scale : __fmul_rn(qs, ks_next[g]);
 
       SAGE_WAIT_OR(s_full + h, j & 1, 8, { ok = false; break; });
       tc_fence_after();
       uint32_t sr[2][32];
       tmem_ld32(t_s, sr[0]);
       tmem_ld32(t_s + 32, sr[1]);
+      if constexpr (!QKF) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const int kg = (kv_base + kHalfN) / 16 + g;
-        ks_next[g] = (kg < p.k_groups) ? __ldg(ks_base + kg) : 0.0f;
+        for (int g = 0; g < 4; ++g) {
+          const int kg = (kv_base + kHalfN) / 16 + g;
+          ks_next[g] = (kg < p.k_groups) ? __ldg(ks_base + kg) : 0.0f;
+        }
       }
       tc_wait_ld();
 
@@ -364,6 +415,11 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
       // p = exp2(s - m), row sum before rounding (:676-689), P -> fp16 pairs.  Returns the sum of
       // the 64 values of this half.
+      // raw accumulator word -> fp32: an int32 product sum (exact), or the fp32 dot product itself
+      auto score_of = [](uint32_t w) -> float {
+        if constexpr (QKF) return __uint_as_float(w);
+        else return __int2float_rn(static_cast<int>(w));
+      };
       uint32_t pk[32];
       f32x2_t cg2[4];
 #pragma unroll
@@ -377,8 +433,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int e = 32 * c + 2 * i;
-            const f32x2_t sf = pack2(__int2float_rn(static_cast<int>(sr[c][2 * i])),
-                                     __int2float_rn(static_cast<int>(sr[c][2 * i + 1])));
+            const f32x2_t sf = pack2(score_of(sr[c][2 * i]), score_of(sr[c][2 * i + 1]));
             const float2 x = unpack2(ffma2(sf, cg2[e >> 4], neg_m));
             float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
             if constexpr (kMasked) {
@@ -412,7 +467,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
       refused_last = attempt && !done;
-      if (!done && !masked) {
+      if (!done && !masked && !QKF) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {                   // scales are >= 0: max commutes with the scaling
           int mx = static_cast<int>(sr[g >> 1][(g & 1) * 16]);
@@ -425,7 +480,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float sv = __int2float_rn(static_cast<int>(sr[c][i])) * cg[(32 * c + i) >> 4];
+            const float sv = score_of(sr[c][i]) * cg[(32 * c + i) >> 4];   // (:1679) for the fp32 scores
             if (32 * c + i < col_end) m_half = fmaxf(m_half, sv);
           }
       }

@@ -86,6 +86,28 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* b
   return SAGE_OK;
 }
 
+// Tiled map of a 16-bit [B,H,S,D] tensor in the caller's layout: dimensions (D, S, H, B) with the
+// caller's element strides, boxes of `box_rows` rows x 64 columns, 128-byte swizzle.  A dimension of
+// extent 1 may carry any stride in the caller's tensor; it gets the span of the others so that the
+// map stays well formed.
+int encode_strided_16bit(CUtensorMap* map, CUtensorMapDataType dt, const void* base, int D, long long S, long long H,
+                         long long B, long long stride_s, long long stride_h, long long stride_b, int box_rows,
+                         const char* what) {
+  cuuint64_t ss = (cuuint64_t)stride_s * 2, sh = (cuuint64_t)stride_h * 2, sb = (cuuint64_t)stride_b * 2;
+  cuuint64_t span = (cuuint64_t)D * 2;
+  if (S > 1 && ss * S > span) span = ss * S;
+  if (H > 1 && sh * H > span) span = sh * H;
+  if (B > 1 && sb * B > span) span = sb * B;
+  span = (span + 15) & ~(cuuint64_t)15;
+  if (S == 1) ss = span;
+  if (H == 1) sh = span;
+  if (B == 1) sb = span;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {ss, sh, sb};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  return encode_map(map, dt, 4, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, what);
+}
+
 template <typename T, int D>
 int launch_prep(const sage::PrepParams& p, int v_blocks, cudaStream_t stream) {
   const int grid = p.q_blocks + p.k_blocks + v_blocks;
@@ -108,11 +130,38 @@ int v_block_count(long long B, long long H, long long S, int D) {
   return static_cast<int>((n_vec + sage::kPrepThreads * 4 - 1) / (sage::kPrepThreads * 4));
 }
 
-template <int D, bool CAUSAL, bool DUMP>
+// The fields of AttnParams that do not depend on the kind of Q / K.
+void fill_attn_params(sage::AttnParams* pp, void* o, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s,
+                      int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv, float* lse, int* status) {
+  sage::AttnParams& p = *pp;
+  memset(&p, 0, sizeof(p));
+  p.o = o; p.o_stride_b = o_stride_b; p.o_stride_h = o_stride_h; p.o_stride_s = o_stride_s;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv;
+  p.q_groups = (Sq + sage::kQGroupRows - 1) / sage::kQGroupRows;
+  p.k_groups = (Skv + sage::kKGroupRows - 1) / sage::kKGroupRows;
+  p.n_q_tiles = (Sq + sage::kBlockM - 1) / sage::kBlockM;
+  // 8 heads at a time (each needs Skv * D * 3 bytes of K and V in L2), whole GQA groups only
+  const int rep = Hq / Hkv;
+  p.head_group = rep * ((8 + rep - 1) / rep);
+  p.out_bf16 = (out_dtype == SAGE_DTYPE_BF16);
+  p.lse = lse;
+  p.status = status;
+  // Every barrier wait in the kernel gives up after this many SM clocks (about one second) and
+  // reports through `status`.  Two environment variables exist for the failure-detection test only:
+  // SAGE_WAIT_LIMIT_US shortens the bound, SAGE_TEST_DROP_V_LOAD makes a wait run out on purpose.
+  p.wait_limit_cycles = sage::kWaitLimitCycles;
+  if (const char* e = getenv("SAGE_WAIT_LIMIT_US")) {
+    const long long us = atoll(e);
+    if (us > 0) p.wait_limit_cycles = us * 2000;        // ~2 GHz
+  }
+  p.test_drop_v_load = (getenv("SAGE_TEST_DROP_V_LOAD") != nullptr) ? 1 : 0;
+}
+
+template <int D, bool CAUSAL, bool DUMP, bool QKF = false, int KST = 0>
 int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                 const sage::AttnParams& p, cudaStream_t stream) {
-  auto kern = sage::sage_attn_kernel<D, CAUSAL, DUMP>;
-  constexpr int kSmem = sage::AttnSmem<D>::kTotal;
+  auto kern = sage::sage_attn_kernel<D, CAUSAL, DUMP, QKF, KST>;
+  constexpr int kSmem = sage::AttnSmem<D, QKF ? 2 : 1, KST>::kTotal;
   static bool configured[64] = {};
   int dev = 0;
   SAGE_CUDA(cudaGetDevice(&dev));
@@ -277,29 +326,9 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
   if (Sq == 0) return SAGE_OK;
 
   sage::AttnParams p;
-  memset(&p, 0, sizeof(p));
+  fill_attn_params(&p, o, o_stride_b, o_stride_h, o_stride_s, out_dtype, B, Hq, Hkv, Sq, Skv, lse, status);
   p.q_scale = q_scale; p.k_scale = k_scale;
-  p.o = o; p.o_stride_b = o_stride_b; p.o_stride_h = o_stride_h; p.o_stride_s = o_stride_s;
-  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv;
-  p.q_groups = (Sq + sage::kQGroupRows - 1) / sage::kQGroupRows;
-  p.k_groups = (Skv + sage::kKGroupRows - 1) / sage::kKGroupRows;
-  p.n_q_tiles = (Sq + sage::kBlockM - 1) / sage::kBlockM;
-  // 8 heads at a time (each needs Skv * D * 3 bytes of K and V in L2), whole GQA groups only
-  const int rep = Hq / Hkv;
-  p.head_group = rep * ((8 + rep - 1) / rep);
-  p.out_bf16 = (out_dtype == SAGE_DTYPE_BF16);
   p.s_dump = s_dump;
-  p.lse = lse;
-  p.status = status;
-  // Every barrier wait in the kernel gives up after this many SM clocks (about one second) and
-  // reports through `status`.  Two environment variables exist for the failure-detection test only:
-  // SAGE_WAIT_LIMIT_US shortens the bound, SAGE_TEST_DROP_V_LOAD makes a wait run out on purpose.
-  p.wait_limit_cycles = sage::kWaitLimitCycles;
-  if (const char* e = getenv("SAGE_WAIT_LIMIT_US")) {
-    const long long us = atoll(e);
-    if (us > 0) p.wait_limit_cycles = us * 2000;        // ~2 GHz
-  }
-  p.test_drop_v_load = (getenv("SAGE_TEST_DROP_V_LOAD") != nullptr) ? 1 : 0;
 
   // With no keys every row has l == 0 and the output is 0 (csrc/attn_gfx11.cu:771).  The kernel
   // handles that without touching K or V, but a tensor map cannot have a zero extent: describe one
@@ -325,42 +354,12 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
     if (rc) return rc;
   }
   {
-    // A dimension of extent 1 may carry any stride in the caller's tensor; give it the span of
-    // the others so that the map stays well formed.
-    cuuint64_t ss = (cuuint64_t)v16->stride_s * 2, sh = (cuuint64_t)v16->stride_h * 2, sb = (cuuint64_t)v16->stride_b * 2;
-    cuuint64_t span = (cuuint64_t)D * 2;
-    if (skv_map > 1 && ss * skv_map > span) span = ss * skv_map;
-    if (Hkv > 1 && sh * Hkv > span) span = sh * Hkv;
-    if (B > 1 && sb * B > span) span = sb * B;
-    span = (span + 15) & ~(cuuint64_t)15;
-    if (skv_map == 1) ss = span;
-    if (Hkv == 1) sh = span;
-    if (B == 1) sb = span;
-    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)skv_map, (cuuint64_t)Hkv, (cuuint64_t)B};
-    cuuint64_t strides[3] = {ss, sh, sb};
-    cuuint32_t box[4] = {64, (cuuint32_t)sage::kBlockN, 1, 1};
-    int rc = encode_map(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, v_base, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B, "v16");
+    int rc = encode_strided_16bit(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, v_base, D, skv_map, Hkv, B, v16->stride_s,
+                                  v16->stride_h, v16->stride_b, sage::kBlockN, "v16");
     if (rc) return rc;
-  }
-
-  {
-    // O in the caller's layout: (D, Sq, Hq, B) with the caller's strides; the kernel stores boxes of
-    // 32 rows x 64 columns.  Extent-1 dimensions get the span of the others, as for V.
-    cuuint64_t ss = (cuuint64_t)o_stride_s * 2, sh = (cuuint64_t)o_stride_h * 2, sb = (cuuint64_t)o_stride_b * 2;
-    cuuint64_t span = (cuuint64_t)D * 2;
-    if (Sq > 1 && ss * Sq > span) span = ss * Sq;
-    if (Hq > 1 && sh * Hq > span) span = sh * Hq;
-    if (B > 1 && sb * B > span) span = sb * B;
-    span = (span + 15) & ~(cuuint64_t)15;
-    if (Sq == 1) ss = span;
-    if (Hq == 1) sh = span;
-    if (B == 1) sb = span;
-    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)Sq, (cuuint64_t)Hq, (cuuint64_t)B};
-    cuuint64_t strides[3] = {ss, sh, sb};
-    cuuint32_t box[4] = {64, 32, 1, 1};
-    int rc = encode_map(&to, p.out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, o,
-                        dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "o");
+    // O in the caller's layout; the kernel stores boxes of 32 rows x 64 columns.
+    rc = encode_strided_16bit(&to, p.out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, o,
+                              D, Sq, Hq, B, o_stride_s, o_stride_h, o_stride_b, 32, "o");
     if (rc) return rc;
   }
   const bool dump = (s_dump != nullptr);
@@ -369,6 +368,63 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
   if (D == 128) return is_causal ? SAGE_LAUNCH(128, true) : SAGE_LAUNCH(128, false);
   return is_causal ? SAGE_LAUNCH(64, true) : SAGE_LAUNCH(64, false);
 #undef SAGE_LAUNCH
+}
+
+int sage_direct_attn(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
+                     int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status, void* stream) {
+  SAGE_REQUIRE(q && q->ptr && v16 && o, "sage_direct_attn: null pointer");
+  SAGE_REQUIRE(Skv == 0 || (k && k->ptr && v16->ptr), "sage_direct_attn: null pointer");
+  SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_direct_attn: dtype must be f16 or bf16");
+  SAGE_REQUIRE(D == 64 || D == 128, "sage_direct_attn: head_dim must be 64 or 128, got %d", D);
+  SAGE_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Sq >= 0 && Skv >= 0, "sage_direct_attn: bad sizes");
+  SAGE_REQUIRE(Hq % Hkv == 0, "sage_direct_attn: Hq (%d) must be a multiple of Hkv (%d)", Hq, Hkv);
+  SAGE_REQUIRE(aligned16(q->ptr) && strides_ok(q), "sage_direct_attn: q needs a 16-byte aligned base and strides % 8 == 0");
+  SAGE_REQUIRE(Skv == 0 || (aligned16(k->ptr) && strides_ok(k) && aligned16(v16->ptr) && strides_ok(v16)),
+               "sage_direct_attn: k / v need 16-byte aligned bases and strides % 8 == 0");
+  SAGE_REQUIRE(aligned16(o) && o_stride_b % 8 == 0 && o_stride_h % 8 == 0 && o_stride_s % 8 == 0,
+               "sage_direct_attn: o needs a 16-byte aligned base and strides % 8 == 0");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (Sq == 0) return SAGE_OK;
+
+  sage::AttnParams p;
+  fill_attn_params(&p, o, o_stride_b, o_stride_h, o_stride_s, dtype, B, Hq, Hkv, Sq, Skv, lse, status);
+  p.qk_bf16 = (dtype == SAGE_DTYPE_BF16);
+  p.score_scale = sm_scale * 1.4426950408889634f;       // csrc/attn_gfx11.cu:34, as for the quantised path
+
+  // No keys: nothing is loaded (see sage_qk_int8_sv_f16_attn_lse); the maps describe one dummy row.
+  const int skv_map = Skv > 0 ? Skv : 1;
+  const void* k_base = Skv > 0 ? k->ptr : q->ptr;
+  const void* v_base = Skv > 0 ? v16->ptr : q->ptr;
+  const sage_strided_t kk = Skv > 0 ? *k : sage_strided_t{q->ptr, 0, 0, (int64_t)D};
+  const sage_strided_t vv = Skv > 0 ? *v16 : sage_strided_t{q->ptr, 0, 0, (int64_t)D};
+  const CUtensorMapDataType qk_dt = p.qk_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+
+  CUtensorMap tq, tk, tv, to;
+  int rc = encode_strided_16bit(&tq, qk_dt, q->ptr, D, Sq, Hq, B, q->stride_s, q->stride_h, q->stride_b, sage::kBlockM, "q");
+  if (rc) return rc;
+  rc = encode_strided_16bit(&tk, qk_dt, k_base, D, skv_map, Hkv, B, kk.stride_s, kk.stride_h, kk.stride_b, sage::kBlockN, "k");
+  if (rc) return rc;
+  rc = encode_strided_16bit(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, v_base, D, skv_map, Hkv, B, vv.stride_s, vv.stride_h,
+                            vv.stride_b, sage::kBlockN, "v16");
+  if (rc) return rc;
+  rc = encode_strided_16bit(&to, qk_dt, o, D, Sq, Hq, B, o_stride_s, o_stride_h, o_stride_b, 32, "o");
+  if (rc) return rc;
+  if (D == 128) {
+    // A grid that cannot put two CTAs on every SM anyway takes the deeper K/V rings (one CTA per SM).
+    int dev = 0, sms = 0;
+    SAGE_CUDA(cudaGetDevice(&dev));
+    SAGE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long ctas = static_cast<long long>(p.n_q_tiles) * B * Hq;
+    if (ctas <= sms) {
+      return is_causal ? launch_attn<128, true, false, true, 2>(tq, tk, tv, to, p, st)
+                       : launch_attn<128, false, false, true, 2>(tq, tk, tv, to, p, st);
+    }
+    return is_causal ? launch_attn<128, true, false, true>(tq, tk, tv, to, p, st)
+                     : launch_attn<128, false, false, true>(tq, tk, tv, to, p, st);
+  }
+  return is_causal ? launch_attn<64, true, false, true>(tq, tk, tv, to, p, st)
+                   : launch_attn<64, false, false, true>(tq, tk, tv, to, p, st);
 }
 
 }  // extern "C"

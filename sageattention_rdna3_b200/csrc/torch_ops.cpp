@@ -208,9 +208,69 @@ at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, c
   return o;
 }
 
+// fp16_attn / bf16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout,
+//                       int value_layout, int is_causal, float sm_scale, int bm_sel, Tensor? status,
+//                       Tensor? lse) -> Tensor
+// Counterparts of fp16_attn_t / bf16_attn_t (csrc/pybind_gfx11.cpp:24-31): the un-quantised kernel
+// for short sequences.  query/key are fp16 (fp16_attn) or bf16 (bf16_attn) in `tensor_layout`;
+// `value` is fp16 [..,S,D] in `value_layout` (the reference passes the transposed fp16 V_T);
+// `bm_sel` picked a tile height on RDNA3 and is accepted and ignored.
+at::Tensor direct_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, int64_t layout,
+                       int64_t value_layout, int64_t is_causal, double sm_scale, int64_t /*bm_sel*/,
+                       const c10::optional<at::Tensor>& status, const c10::optional<at::Tensor>& lse,
+                       at::ScalarType want, const char* name) {
+  TORCH_CHECK(q.scalar_type() == want && k.scalar_type() == want && o.scalar_type() == want, name,
+              ": query, key and output must be ", want);
+  TORCH_CHECK(v.scalar_type() == at::kHalf, name, ": value must be fp16 (convert bf16 with v_to_f16)");
+  check_16b(q, "query");
+  check_16b(k, "key");
+  check_16b(v, "value");
+  check_16b(o, "output");
+  const Dims dq = dims_of(q, layout), dk = dims_of(k, layout), dv = dims_of(v, value_layout), d_o = dims_of(o, layout);
+  TORCH_CHECK(dk.B == dq.B && dk.D == dq.D, "query/key batch or head_dim mismatch");
+  TORCH_CHECK(dv.B == dk.B && dv.H == dk.H && dv.S == dk.S && dv.D == dk.D, "value shape does not match key");
+  TORCH_CHECK(d_o.B == dq.B && d_o.H == dq.H && d_o.S == dq.S && d_o.D == dq.D, "output shape does not match query");
+  TORCH_CHECK(dq.D == 64 || dq.D == 128, "head_dim must be 64 or 128, got ", dq.D);
+  TORCH_CHECK(dk.H > 0 && dq.H % dk.H == 0, "num_qo_heads must be a multiple of num_kv_heads");
+  int* status_ptr = nullptr;
+  if (status.has_value()) {
+    TORCH_CHECK(status->scalar_type() == at::kInt && status->numel() >= 1 && status->is_cuda(), "status must be an int32 CUDA tensor");
+    status_ptr = status->data_ptr<int>();
+  }
+  float* lse_ptr = nullptr;
+  if (lse.has_value()) {
+    TORCH_CHECK(lse->scalar_type() == at::kFloat && lse->is_contiguous() && lse->numel() == dq.B * dq.H * dq.S && lse->is_cuda(),
+                "lse must be a contiguous fp32 CUDA tensor [B,Hq,Sq]");
+    lse_ptr = lse->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(q.device());
+  const sage_strided_t qs = strided_of(q, layout), ks = strided_of(k, layout), vs = strided_of(v, value_layout);
+  const sage_strided_t os = strided_of(o, layout);
+  check_rc(sage_direct_attn(&qs, &ks, &vs, o.data_ptr(), os.stride_b, os.stride_h, os.stride_s, dtype_code(q), (int)dq.B,
+                            (int)dq.H, (int)dk.H, (int)dq.S, (int)dk.S, (int)dq.D, (int)is_causal, (float)sm_scale,
+                            lse_ptr, status_ptr, current_stream(q)),
+           name);
+  return o;
+}
+at::Tensor fp16_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, int64_t layout,
+                     int64_t value_layout, int64_t is_causal, double sm_scale, int64_t bm_sel,
+                     const c10::optional<at::Tensor>& status, const c10::optional<at::Tensor>& lse) {
+  return direct_attn(q, k, v, o, layout, value_layout, is_causal, sm_scale, bm_sel, status, lse, at::kHalf, "fp16_attn");
+}
+at::Tensor bf16_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, int64_t layout,
+                     int64_t value_layout, int64_t is_causal, double sm_scale, int64_t bm_sel,
+                     const c10::optional<at::Tensor>& status, const c10::optional<at::Tensor>& lse) {
+  return direct_attn(q, k, v, o, layout, value_layout, is_causal, sm_scale, bm_sel, status, lse, at::kBFloat16,
+                     "bf16_attn");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(sageattention, m) {
+  m.def("fp16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
+        "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
+  m.def("bf16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
+        "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("qk_int8_sv_f16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor q_scale, "
         "Tensor k_scale, int tensor_layout, int value_layout, int is_causal, float sm_scale, "
         "Tensor? s_dump=None, Tensor? status=None, Tensor? lse=None) -> Tensor");
@@ -223,6 +283,8 @@ TORCH_LIBRARY(sageattention, m) {
 
 TORCH_LIBRARY_IMPL(sageattention, CUDA, m) {
   m.impl("qk_int8_sv_f16_attn", &qk_int8_sv_f16_attn);
+  m.impl("fp16_attn", &fp16_attn);
+  m.impl("bf16_attn", &bf16_attn);
   m.impl("quant_qk_int8", &quant_qk_int8);
   m.impl("prep_qkv", &prep_qkv);
   m.impl("mean_seq", &mean_seq);

@@ -24,7 +24,8 @@ def _unit_chunks(batch: int, hkv: int, rep: int, want: int) -> List[Tuple[int, i
 
 def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
                   tensor_layout: str = "HND", is_causal: bool = False, sm_scale: Optional[float] = None,
-                  smooth_k: bool = False, device: Optional[torch.device] = None, chunks: int = 8) -> torch.Tensor:
+                  smooth_k: bool = False, device: Optional[torch.device] = None, chunks: int = 8,
+                  **kwargs) -> torch.Tensor:
     """q, k, v: CPU tensors (pinned memory for asynchronous copies) in ``tensor_layout``; returns a
     pinned CPU tensor shaped like q (or fills ``out``).  With "HND" the work is cut along batch and
     heads; "NHD" head slices are not contiguous in host memory, so it is cut along the batch only."""
@@ -67,7 +68,8 @@ def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Option
         with torch.cuda.stream(s_run):
             s_run.wait_event(copied)
             od = sageattn(qd_all[q_idx].unsqueeze(0), kd_all[kv_idx].unsqueeze(0), vd_all[kv_idx].unsqueeze(0),
-                          tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k)
+                          tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k,
+                          **kwargs)
             computed = torch.cuda.Event()
             computed.record(s_run)
         with torch.cuda.stream(s_out):

@@ -72,12 +72,14 @@ def from_units(o_units: torch.Tensor, batch: int, num_qo_heads: int, tensor_layo
 
 def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                      is_causal: bool = False, sm_scale: Optional[float] = None, smooth_k: bool = False,
-                     group=None, gather: bool = True, attn_fn: Optional[Callable] = None):
+                     group=None, gather: bool = True, attn_fn: Optional[Callable] = None, **kwargs):
     """Run this rank's share of ``sageattn(q, k, v)`` and optionally all-gather the outputs.
 
     Every rank passes the same global ``q, k, v`` (or at least its own units filled in).  Returns the
     full output in the caller's layout when ``gather`` is true, otherwise this rank's units
-    ``[n, Hq/Hkv, Sq, D]`` and its :class:`Shard`.  ``attn_fn`` defaults to :func:`sageattn`.
+    ``[n, Hq/Hkv, Sq, D]`` and its :class:`Shard`.  ``attn_fn`` defaults to :func:`sageattn`; other
+    keyword arguments go to it.  The choice between the INT8 and the un-quantised kernel is made
+    here, from the caller's shapes and layout, so that every rank and the unsharded call agree.
     """
     import torch.distributed as dist
     if attn_fn is None:
@@ -90,8 +92,14 @@ def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_l
     shards = plan_shards(B, hq, hkv, world)
     mine = shards[rank]
     ql, kl, vl = shard_inputs(q, k, v, tensor_layout, mine)
+    if "kernel" not in kwargs:
+        from .core import use_direct_kernel
+        s_dim = 2 if tensor_layout == "HND" else 1
+        direct = use_direct_kernel(q.size(-1), tensor_layout, is_causal, q.size(s_dim), k.size(s_dim))
+        kwargs["kernel"] = "direct" if direct else "int8"
     if mine.n_units > 0:
-        o_local = attn_fn(ql, kl, vl, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k)
+        o_local = attn_fn(ql, kl, vl, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k,
+                          **kwargs)
     else:
         o_local = ql.new_empty(ql.shape)
     if not gather:

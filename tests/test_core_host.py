@@ -66,3 +66,43 @@ def test_units_roundtrip_keeps_gqa_groups_together(layout):
     ql, kl, vl = shard_inputs(q, k, k, layout, Shard(1, 2, 5))
     assert ql.shape == (3, 2, S, D) and kl.shape == (3, 1, S, D)
     assert torch.equal(kl[:, 0], k_hnd.reshape(B * Hkv, S, D)[2:5])
+
+
+def test_kernel_dispatch_table_of_the_reference(monkeypatch):
+    """``use_direct_kernel`` reproduces ``sageattention/core.py:113-139`` case by case."""
+    from sageattention_rdna3_b200.core import use_direct_kernel as ud
+    for name in ("SAGEATTN_KERNEL", "SAGEATTN_DIRECT_THRESHOLD_D64", "SAGEATTN_DIRECT_THRESHOLD_D64_CAUSAL",
+                 "SAGEATTN_DIRECT_THRESHOLD_D64_CROSS", "SAGEATTN_DIRECT_THRESHOLD_D128",
+                 "SAGEATTN_DIRECT_THRESHOLD_D128_CROSS"):
+        monkeypatch.delenv(name, raising=False)
+    # head_dim 64, self attention: 2048 in HND, 3072 in NHD (core.py:121-124,132)
+    assert ud(64, "HND", False, 2048, 2048) and not ud(64, "HND", False, 2049, 2049)
+    assert ud(64, "NHD", False, 3072, 3072) and not ud(64, "NHD", False, 3073, 3073)
+    # causal: 6144 (core.py:125-126); cross (q shorter than kv): 6144 (core.py:127-129)
+    assert ud(64, "HND", True, 6144, 6144) and not ud(64, "HND", True, 6145, 6145)
+    assert ud(64, "NHD", False, 3072, 4096) and not ud(64, "NHD", False, 100, 6145)
+    # head_dim 128: 2048, and 4096 when q is less than half of kv (core.py:133-139)
+    assert ud(128, "HND", False, 2048, 2048) and not ud(128, "HND", True, 2049, 2049)
+    assert ud(128, "HND", False, 512, 4096) and not ud(128, "HND", False, 2048, 4096)
+    assert not ud(128, "NHD", False, 512, 4097)
+    # the five BASELINE configurations: 1 -> un-quantised, 2..5 -> INT8
+    assert ud(64, "HND", False, 1024, 1024)
+    assert not ud(64, "NHD", False, 4096, 4096) and not ud(128, "HND", True, 8192, 8192)
+    assert not ud(128, "HND", True, 4096, 4096) and not ud(128, "NHD", False, 32768, 32768)
+    # overrides
+    monkeypatch.setenv("SAGEATTN_DIRECT_THRESHOLD_D128", "0")
+    assert not ud(128, "HND", False, 64, 64)
+    monkeypatch.setenv("SAGEATTN_KERNEL", "direct")
+    assert ud(128, "HND", False, 8192, 8192)
+
+
+def test_direct_emulation_against_fp32_sdpa():
+    from oracle import sage_oracle as so
+    g = torch.Generator().manual_seed(0)
+    for dtype, causal, layout in ((torch.float16, False, "HND"), (torch.bfloat16, True, "NHD")):
+        shape = (1, 3, 150, 64) if layout == "HND" else (1, 150, 3, 64)
+        q, k, v = (torch.randn(shape, generator=g).to(dtype) for _ in range(3))
+        o = so.direct_attn_emulated(q, k, v, tensor_layout=layout, is_causal=causal)
+        ref = so.sdpa_fp32(q, k, v, tensor_layout=layout, is_causal=causal)
+        acc = so.accuracy(o.float(), ref)
+        assert o.dtype == dtype and acc["cos"] > 0.9999 and acc["max_abs"] < 2e-2, acc

@@ -130,7 +130,10 @@ def test_attention_int32_scores_bit_exact_and_output_close(dev, case):
 
 
 def _public(q, k, v, dev, **kw):
+    """``sageattn`` on the INT8 kernel unless the test says otherwise (short shapes would take the
+    un-quantised kernel by default, which has its own tests below)."""
     from sageattention_rdna3_b200 import check_status, sageattn
+    kw.setdefault("kernel", "int8")
     o = sageattn(q.to(dev), k.to(dev), v.to(dev), **kw)
     check_status(dev)
     return o
@@ -372,9 +375,10 @@ def test_lse_matches_oracle_and_fp32(dev, case):
     sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
     q, k, v = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype, offset=off), H.randn(sk, 2, dtype)
     o, lse = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=causal, smooth_k=smooth,
-                      return_lse=True)
+                      return_lse=True, kernel="int8")
     check_status(dev)
-    o_plain = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=causal, smooth_k=smooth)
+    o_plain = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=causal, smooth_k=smooth,
+                       kernel="int8")
     assert torch.equal(o, o_plain)                               # asking for lse does not change O
     assert lse.shape == (B, Hq, Sq) and lse.dtype == torch.float32
     o_emu, lse_emu = so.sageattn_emulated(q, k, v, tensor_layout=layout, is_causal=causal, smooth_k=smooth,
@@ -419,3 +423,84 @@ def test_lse_through_the_c_abi_and_merge_of_two_kv_halves(dev):
     assert (lm - lse_all).abs().max().item() < 1e-3
     acc = so.accuracy(merged, o_all)
     assert acc["cos"] >= 0.99999 and acc["max_abs"] < 2e-3, acc
+
+
+# ----------------------------------------------------------------------------------------------
+# The un-quantised kernel for short sequences (the reference's fp16_attn_t / bf16_attn_t branch).
+# The order of additions inside a tensor-core dot product is not defined, so everything here is by
+# tolerance: against the emulation of that branch (cos >= 0.999, rel L1 <= 1e-2; measured 1e-4) and
+# against fp32 SDPA with the reference's own gates.
+DIRECT_CASES = [
+    # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, sm_scale
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, None),     # BASELINE config 1: the reference runs it here
+    (1, 2, 2, 1024, 1024, 128, torch.bfloat16, "HND", True, None),
+    (2, 4, 2, 300, 333, 128, torch.bfloat16, "NHD", False, None),     # GQA, ragged, cross lengths
+    (1, 3, 3, 33, 65, 64, torch.bfloat16, "HND", True, 0.5),
+    (2, 8, 2, 512, 77, 64, torch.float16, "NHD", False, None),        # text-encoder cross attention (kv = 77)
+    (1, 4, 4, 2048, 154, 128, torch.float16, "HND", False, None),
+    (1, 4, 1, 777, 777, 128, torch.float16, "NHD", True, None),
+    (1, 2, 2, 128, 2048, 128, torch.float16, "HND", False, None),     # one query tile: the two-stage variant
+    (1, 160, 160, 128, 256, 128, torch.bfloat16, "HND", False, None), # > 148 CTAs: the one-stage variant
+    (1, 1, 1, 1, 1, 64, torch.float16, "HND", False, None),
+]
+
+
+def abi_direct(q, k, v16, v_layout, layout, causal, sm, want_lse=True):
+    import ctypes
+    lib = H._native.load_abi()
+    B, Hq, Sq, D = H.dims(q, layout)
+    _, Hkv, Skv, _ = H.dims(k, layout)
+    o = torch.full(q.shape, float("nan"), dtype=q.dtype, device=q.device)
+    lse = torch.full((B, Hq, Sq), float("nan"), dtype=torch.float32, device=q.device) if want_lse else None
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    qs, ks, vs, os_ = H.strided(q, layout), H.strided(k, layout), H.strided(v16, v_layout), H.strided(o, layout)
+    rc = lib.sage_direct_attn(ctypes.byref(qs), ctypes.byref(ks), ctypes.byref(vs), o.data_ptr(), os_.stride_b,
+                              os_.stride_h, os_.stride_s, H.dtype_code(q), B, Hq, Hkv, Sq, Skv, D, int(causal),
+                              ctypes.c_float(sm), lse.data_ptr() if want_lse else None, status.data_ptr(), H._stream())
+    assert rc == 0, lib.sage_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return o, lse
+
+
+@pytest.mark.parametrize("case", DIRECT_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_direct_kernel_through_the_c_abi(dev, case):
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, sm = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k, v = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype), H.randn(sk, 2, dtype)
+    sm_f = sm if sm is not None else D ** -0.5
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    if dtype == torch.bfloat16:
+        v16, v_layout = H.abi_v_to_f16(vd, layout), "HND"
+    else:
+        v16, v_layout = vd, layout
+    o, lse = abi_direct(qd, kd, v16, v_layout, layout, causal, sm_f)
+    emu, lse_emu = so.direct_attn_emulated(q, k, v, tensor_layout=layout, is_causal=causal, sm_scale=sm, return_lse=True)
+    acc = so.accuracy(o.cpu().float(), emu.float())
+    assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, acc
+    assert (lse.cpu() - lse_emu).abs().max().item() < 1e-3
+    ref = so.sdpa_fp32(q, k, v, tensor_layout=layout, is_causal=causal, sm_scale=sm)
+    acc2 = so.accuracy(o.cpu().float(), ref)
+    assert acc2["cos"] > (0.99 if dtype == torch.float16 else 0.98) and acc2["max_abs"] < 0.35, acc2
+
+
+def test_dispatch_follows_the_reference(dev, monkeypatch):
+    """Default call: short kv -> un-quantised kernel, long kv -> INT8 (sageattention/core.py:113-139);
+    keyword and environment overrides; smooth_k is ignored by the un-quantised branch as there."""
+    from sageattention_rdna3_b200 import sageattn
+    q, k, v = (H.randn((1, 2, 512, 64), s, torch.float16).to(dev) for s in (0, 1, 2))
+    o_auto = sageattn(q, k, v)
+    o_direct = sageattn(q, k, v, kernel="direct")
+    o_int8 = sageattn(q, k, v, kernel="int8")
+    assert torch.equal(o_auto, o_direct) and not torch.equal(o_auto, o_int8)
+    assert torch.equal(sageattn(q, k, v, smooth_k=True), o_direct)
+    monkeypatch.setenv("SAGEATTN_KERNEL", "int8")
+    assert torch.equal(sageattn(q, k, v), o_int8)
+    monkeypatch.delenv("SAGEATTN_KERNEL")
+    monkeypatch.setenv("SAGEATTN_DIRECT_THRESHOLD_D64", "256")           # the reference's own knob
+    assert torch.equal(sageattn(q, k, v), o_int8)
+    monkeypatch.delenv("SAGEATTN_DIRECT_THRESHOLD_D64")
+    ql, kl, vl = (H.randn((1, 1, 2304, 128), s, torch.float16).to(dev) for s in (0, 1, 2))
+    assert torch.equal(sageattn(ql, kl, vl), sageattn(ql, kl, vl, kernel="int8"))   # 2304 > 2048
+    with pytest.raises(AssertionError, match="kernel must be"):
+        sageattn(q, k, v, kernel="fp8")

@@ -19,13 +19,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _oracle_attn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=False):
+def _oracle_attn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=False, kernel="int8"):
     from oracle import sage_oracle as so
+    if kernel == "direct":
+        return so.direct_attn_emulated(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale)
     return so.sageattn_emulated(q, k, v, tensor_layout=tensor_layout, is_causal=is_causal, sm_scale=sm_scale,
                                 smooth_k=smooth_k)
 
 
-def _worker(rank, world, port, layout, B, Hq, Hkv, result_dir):
+def _worker(rank, world, port, layout, B, Hq, Hkv, kernel, result_dir):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     torch.set_num_threads(2)
@@ -38,26 +40,29 @@ def _worker(rank, world, port, layout, B, Hq, Hkv, result_dir):
         S, D = 48, 64
         shp = (lambda h: (B, h, S, D)) if layout == "HND" else (lambda h: (B, S, h, D))
         q, k, v = randn(shp(Hq), 0, torch.float16), randn(shp(Hkv), 1, torch.float16), randn(shp(Hkv), 2, torch.float16)
-        out = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, attn_fn=_oracle_attn)
+        kw = {} if kernel == "auto" else {"kernel": kernel}      # "auto": S = 48 resolves to the un-quantised kernel
+        out = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, attn_fn=_oracle_attn, **kw)
         local, shard = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True,
-                                        attn_fn=_oracle_attn, gather=False)
+                                        attn_fn=_oracle_attn, gather=False, **kw)
         torch.save({"out": out, "n_local": shard.n_units, "local_shape": tuple(local.shape)},
                    os.path.join(result_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("layout,B,Hq,Hkv", [("HND", 1, 4, 2), ("NHD", 1, 6, 3)])
-def test_two_ranks_reproduce_single_process(tmp_path, layout, B, Hq, Hkv):
+@pytest.mark.parametrize("layout,B,Hq,Hkv,kernel", [("HND", 1, 4, 2, "int8"), ("NHD", 1, 6, 3, "int8"),
+                                                    ("NHD", 2, 4, 1, "auto")])
+def test_two_ranks_reproduce_single_process(tmp_path, layout, B, Hq, Hkv, kernel):
     world = 2
     port = _free_port()
-    mp.spawn(_worker, args=(world, port, layout, B, Hq, Hkv, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, layout, B, Hq, Hkv, kernel, str(tmp_path)), nprocs=world, join=True)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from helpers import randn
     S, D = 48, 64
     shp = (lambda h: (B, h, S, D)) if layout == "HND" else (lambda h: (B, S, h, D))
     q, k, v = randn(shp(Hq), 0, torch.float16), randn(shp(Hkv), 1, torch.float16), randn(shp(Hkv), 2, torch.float16)
-    want = _oracle_attn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True)
+    want = _oracle_attn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True,
+                        kernel="direct" if kernel == "auto" else kernel)
     units = 0
     for r in range(world):
         got = torch.load(os.path.join(str(tmp_path), f"rank{r}.pt"))
