@@ -55,6 +55,8 @@ int sage_mean_seq(const sage_strided_t* k, int dtype, int B, int H, int S, int D
  * ([B,Hkv,D], input dtype; may be NULL) subtracted in fp32 first.
  * Outputs: q_i8 [B,Hq,Sq,D], k_i8 [B,Hkv,Skv,D] (int8, contiguous), q_scale [B,Hq,ceil(Sq/32)],
  * k_scale [B,Hkv,ceil(Skv/16)] (fp32).
+ * Sq == 0 or Skv == 0 quantises one side only (the pointers of the empty side are not looked
+ * at): K once, Q per call, for keys that are reused.
  * If `v` and `v16` are both non-NULL the same launch also writes v16 = fp16(v), [B,Hkv,Skv,D]
  * contiguous: the dtype half of v_transpose_gfx11 (csrc/attn_gfx11.h:51; csrc/attn_gfx11.cu:377-381). */
 int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const void* k_mean,

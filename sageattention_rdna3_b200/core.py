@@ -2,10 +2,11 @@
 (``sageattention/core.py:40-233``) in front of hand-written sm_100a kernels.
 
 Same call, same defaults, same assertions as the reference.  What is gone: the Triton default and
-the ``SAGEATTN_BACKEND`` switch (``core.py:8,68-76``), the un-quantised "direct" kernels and their
-size thresholds (``core.py:113-163``) and the transposed V scratch (``core.py:173-180``).  Every
-call runs the INT8 path: [K mean] -> quantise Q/K (+ fp16 copy of a bf16 V) -> fused attention.
-There is no CPU or PyTorch fallback; without the compiled extension the call raises.
+the ``SAGEATTN_BACKEND`` switch (``core.py:8,68-76``) and the transposed V scratch
+(``core.py:173-180``).  A call runs either the INT8 path - [K mean] -> quantise Q/K (+ fp16 copy of a
+bf16 V) -> fused attention - or, for the short sequences the reference sends there
+(``core.py:113-163``), the un-quantised kernel.  There is no CPU or PyTorch fallback; without the
+compiled extension the call raises.
 """
 from __future__ import annotations
 
@@ -47,7 +48,8 @@ def check_status(device: Union[torch.device, int, None] = None) -> None:
 
 
 def _aligned(t: torch.Tensor) -> bool:
-    return t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])
+    s0, s1, s2, _ = t.stride()
+    return (s0 | s1 | s2) % 8 == 0 and t.data_ptr() % 16 == 0
 
 
 # Largest kv length that goes to the un-quantised kernel, per case of the reference's dispatch
@@ -132,9 +134,10 @@ def sageattn(
     assert tensor_layout in _LAYOUT_CODE, f"tensor_layout must be 'HND' or 'NHD', got {tensor_layout!r}."
     assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4, "q, k, v must be 4-D tensors."
 
-    headdim = q.size(-1)
+    q_shape, k_shape, q_stride = q.shape, k.shape, q.stride()    # read once: each call costs ~0.3 us
+    headdim = q_shape[3]
     assert headdim in [64, 128], f"head_dim must be 64 or 128, got {headdim}."
-    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1, (
+    assert q_stride[3] == 1 and k.stride(3) == 1 and v.stride(3) == 1, (
         "Last dim of qkv must be contiguous."
     )
     if sm_scale is None:
@@ -144,9 +147,10 @@ def sageattn(
     if dtype == torch.float32:
         q, k, v = q.to(torch.float16), k.to(torch.float16), v.to(torch.float16)
         dtype = torch.float16
+        q_stride = q.stride()
 
     # core.py:91-95: the output inherits q's strides and is written with 16-byte vector stores.
-    assert q.stride(0) % 8 == 0 and q.stride(1) % 8 == 0 and q.stride(2) % 8 == 0, (
+    assert q_stride[0] % 8 == 0 and q_stride[1] % 8 == 0 and q_stride[2] % 8 == 0, (
         "native backend requires q strides that are multiples of 8 halfs "
         "(16B aligned write-back). "
         f"Got strides={q.stride()}. Use contiguous tensors."
@@ -154,9 +158,9 @@ def sageattn(
     ops = _native.load_ops()
     layout = _LAYOUT_CODE[tensor_layout]
     seq_dim, head_dim_idx = (2, 1) if tensor_layout == "HND" else (1, 2)
-    q_len, kv_len = q.size(seq_dim), k.size(seq_dim)
-    assert k.shape == v.shape, "k and v must have the same shape."
-    assert q.size(0) == k.size(0) and q.size(head_dim_idx) % max(k.size(head_dim_idx), 1) == 0, (
+    q_len, kv_len = q_shape[seq_dim], k_shape[seq_dim]
+    assert k_shape == v.shape, "k and v must have the same shape."
+    assert q_shape[0] == k_shape[0] and q_shape[head_dim_idx] % max(k_shape[head_dim_idx], 1) == 0, (
         "batch sizes must match and num_qo_heads must be a multiple of num_kv_heads."
     )
     # 16-byte vector loads and TMA need aligned bases and strides; the reference leaves that to
@@ -172,51 +176,50 @@ def sageattn(
     lse = None
     want_lse = return_lse and os.environ.get("SAGEATTN_B200_LSE_ZEROS", "0") != "1"
     if return_lse:
-        lse_shape = (q.size(0), q.size(head_dim_idx), q_len)
+        lse_shape = (q_shape[0], q_shape[head_dim_idx], q_len)
         if want_lse:
             lse = torch.full(lse_shape, float("-inf"), dtype=torch.float32, device=q.device)
         else:
             lse = torch.zeros(lse_shape, dtype=torch.float32, device=q.device)
-    if q_len == 0 or q.size(0) == 0 or q.size(head_dim_idx) == 0:
+    if q_len == 0 or q_shape[0] == 0 or q_shape[head_dim_idx] == 0:
         pass
     elif kv_len == 0:
         o.zero_()                        # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
     elif _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len):
-        with torch.cuda.device(q.device):
-            # core.py:141-163: V as fp16 (converted for bf16 inputs), then fp16_attn / bf16_attn
-            if dtype == torch.bfloat16:
-                v16, v_layout = ops.v_to_f16(v, layout), _LAYOUT_CODE["HND"]
-                op = ops.bf16_attn
-            else:
-                v16, v_layout = v, layout
-                op = ops.fp16_attn
-            op(q, k, v16, o, layout, v_layout, int(is_causal), sm_scale, 0, _status_word(q.device),
-               lse if want_lse else None)
+        # core.py:141-163: V as fp16 (converted for bf16 inputs), then fp16_attn / bf16_attn.
+        # (The operators set the device guard themselves; nothing here depends on the current device.)
+        if dtype == torch.bfloat16:
+            v16, v_layout = ops.v_to_f16(v, layout), _LAYOUT_CODE["HND"]
+            op = ops.bf16_attn
+        else:
+            v16, v_layout = v, layout
+            op = ops.fp16_attn
+        op(q, k, v16, o, layout, v_layout, int(is_causal), sm_scale, 0, _status_word(q.device),
+           lse if want_lse else None)
         if os.environ.get("SAGEATTN_B200_CHECK_STATUS", "0") == "1":
             check_status(q.device)
     else:
-        with torch.cuda.device(q.device):
-            if smooth_k:
-                k_mean = ops.mean_seq(k, layout)
-            else:
-                k_mean = torch.empty(0, device=q.device, dtype=q.dtype)
-            if dtype == torch.bfloat16:
-                # P.V runs in fp16 (csrc/attn_gfx11.cu:377-381): one launch quantises Q/K and
-                # writes the fp16 copy of V, [B,Hkv,Skv,D] contiguous.
-                q_int8, q_scale, k_int8, k_scale, v16 = ops.prep_qkv(q, k, v, k_mean, layout, sm_scale)
-                v_layout = _LAYOUT_CODE["HND"]
-            else:
-                q_int8, q_scale, k_int8, k_scale = ops.quant_qk_int8(q, k, k_mean, layout, sm_scale)
-                v16, v_layout = v, layout
-            ops.qk_int8_sv_f16_attn(q_int8, k_int8, v16, o, q_scale, k_scale, layout, v_layout,
-                                    int(is_causal), sm_scale, None, _status_word(q.device),
-                                    lse if want_lse else None)
-            if want_lse and smooth_k:
-                # the kernel saw k - mean: every score of a row was lowered by sm_scale * q.mean
-                rep = q.size(head_dim_idx) // k.size(head_dim_idx)
-                km = k_mean.float().repeat_interleave(rep, dim=1)                   # [B,Hq,D]
-                eq = "bhsd,bhd->bhs" if tensor_layout == "HND" else "bshd,bhd->bhs"
-                lse += torch.einsum(eq, q.float(), km) * sm_scale
+        if smooth_k:
+            k_mean = ops.mean_seq(k, layout)
+        else:
+            k_mean = torch.empty(0, device=q.device, dtype=q.dtype)
+        if dtype == torch.bfloat16:
+            # P.V runs in fp16 (csrc/attn_gfx11.cu:377-381): one launch quantises Q/K and
+            # writes the fp16 copy of V, [B,Hkv,Skv,D] contiguous.
+            q_int8, q_scale, k_int8, k_scale, v16 = ops.prep_qkv(q, k, v, k_mean, layout, sm_scale)
+            v_layout = _LAYOUT_CODE["HND"]
+        else:
+            q_int8, q_scale, k_int8, k_scale = ops.quant_qk_int8(q, k, k_mean, layout, sm_scale)
+            v16, v_layout = v, layout
+        ops.qk_int8_sv_f16_attn(q_int8, k_int8, v16, o, q_scale, k_scale, layout, v_layout,
+                                int(is_causal), sm_scale, None, _status_word(q.device),
+                                lse if want_lse else None)
+        if want_lse and smooth_k:
+            # the kernel saw k - mean: every score of a row was lowered by sm_scale * q.mean
+            rep = q.size(head_dim_idx) // k.size(head_dim_idx)
+            km = k_mean.float().repeat_interleave(rep, dim=1)                   # [B,Hq,D]
+            eq = "bhsd,bhd->bhs" if tensor_layout == "HND" else "bshd,bhd->bhs"
+            lse += torch.einsum(eq, q.float(), km) * sm_scale
         if os.environ.get("SAGEATTN_B200_CHECK_STATUS", "0") == "1":
             check_status(q.device)
 

@@ -228,14 +228,17 @@ int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const v
                        const sage_strided_t* v, void* v16, int dtype, int B, int Hq, int Hkv, int Sq, int Skv,
                        int D, float sm_scale, int8_t* q_i8, float* q_scale, int8_t* k_i8, float* k_scale,
                        void* stream) {
-  SAGE_REQUIRE(q && k && q->ptr && k->ptr, "sage_quant_qk_int8: null input");
-  SAGE_REQUIRE(q_i8 && q_scale && k_i8 && k_scale, "sage_quant_qk_int8: null output");
+  // One side may be empty (Sq == 0 or Skv == 0): its pointers are not looked at.  That is how a
+  // caller quantises K once and Q per call.
+  SAGE_REQUIRE(Sq <= 0 || (q && q->ptr && q_i8 && q_scale), "sage_quant_qk_int8: null q pointer");
+  SAGE_REQUIRE(Skv <= 0 || (k && k->ptr && k_i8 && k_scale), "sage_quant_qk_int8: null k pointer");
   SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_quant_qk_int8: dtype must be f16 or bf16");
   SAGE_REQUIRE(D == 64 || D == 128, "sage_quant_qk_int8: head_dim must be 64 or 128, got %d", D);
   SAGE_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Sq >= 0 && Skv >= 0, "sage_quant_qk_int8: bad sizes");
-  SAGE_REQUIRE(aligned16(q->ptr) && strides_ok(q), "sage_quant_qk_int8: q needs a 16-byte aligned base and strides % 8 == 0");
-  SAGE_REQUIRE(aligned16(k->ptr) && strides_ok(k), "sage_quant_qk_int8: k needs a 16-byte aligned base and strides % 8 == 0");
-  SAGE_REQUIRE(aligned16(q_i8) && aligned16(k_i8), "sage_quant_qk_int8: int8 outputs must be 16-byte aligned");
+  SAGE_REQUIRE(Sq == 0 || (aligned16(q->ptr) && strides_ok(q) && aligned16(q_i8)),
+               "sage_quant_qk_int8: q needs a 16-byte aligned base and strides % 8 == 0, q_i8 a 16-byte aligned base");
+  SAGE_REQUIRE(Skv == 0 || (aligned16(k->ptr) && strides_ok(k) && aligned16(k_i8)),
+               "sage_quant_qk_int8: k needs a 16-byte aligned base and strides % 8 == 0, k_i8 a 16-byte aligned base");
   SAGE_REQUIRE(k_mean == nullptr || aligned16(k_mean), "sage_quant_qk_int8: k_mean must be 16-byte aligned");
   const bool do_v = (v != nullptr && v16 != nullptr);
   if (do_v) {
@@ -244,8 +247,8 @@ int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const v
   }
   sage::PrepParams p;
   memset(&p, 0, sizeof(p));
-  p.q = view_of(q);
-  p.k = view_of(k);
+  if (Sq > 0) p.q = view_of(q);
+  if (Skv > 0) p.k = view_of(k);
   if (do_v) p.v = view_of(v);
   p.q_i8 = q_i8; p.k_i8 = k_i8; p.q_scale = q_scale; p.k_scale = k_scale;
   p.k_mean = k_mean;

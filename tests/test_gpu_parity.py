@@ -504,3 +504,39 @@ def test_dispatch_follows_the_reference(dev, monkeypatch):
     assert torch.equal(sageattn(ql, kl, vl), sageattn(ql, kl, vl, kernel="int8"))   # 2304 > 2048
     with pytest.raises(AssertionError, match="kernel must be"):
         sageattn(q, k, v, kernel="fp8")
+
+
+# ----------------------------------------------------------------------------------------------
+# Keys and values quantised once (quantize_kv) and used by many queries.
+@pytest.mark.parametrize("case", [
+    # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth_k
+    (2, 4, 2, 300, 333, 128, torch.bfloat16, "NHD", False, True),
+    (1, 8, 8, 1024, 77, 64, torch.float16, "HND", False, False),
+    (1, 4, 1, 640, 640, 128, torch.bfloat16, "HND", True, True),
+    (1, 2, 2, 130, 512, 64, torch.float16, "NHD", False, True),
+], ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_quantized_kv_is_bit_identical_to_sageattn(dev, case):
+    from sageattention_rdna3_b200 import check_status, quantize_kv, sageattn, sageattn_quantized_kv
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    k, v = H.randn(sk, 1, dtype, offset=1.0).to(dev), H.randn(sk, 2, dtype).to(dev)
+    kv = quantize_kv(k, v, tensor_layout=layout, smooth_k=smooth)
+    assert kv.k_int8.shape == (B, Hkv, Skv, D) and kv.kv_len == Skv and (kv.k_mean is not None) == smooth
+    for seed in (0, 7):                                        # two different queries against one cache
+        q = H.randn(sq, seed, dtype).to(dev)
+        want, lse_want = sageattn(q, k, v, tensor_layout=layout, is_causal=causal, smooth_k=smooth, kernel="int8",
+                                  return_lse=True)
+        got, lse = sageattn_quantized_kv(q, kv, is_causal=causal, return_lse=True)
+        assert torch.equal(got, want) and torch.equal(lse, lse_want)
+        assert torch.equal(sageattn_quantized_kv(q, kv, is_causal=causal), want)
+    check_status(dev)
+
+
+def test_one_sided_quantisation_through_the_c_abi(dev):
+    """Sq == 0 / Skv == 0 in sage_quant_qk_int8: the other side's results do not change."""
+    q, k = H.randn((1, 2, 100, 64), 0, torch.float16).to(dev), H.randn((1, 2, 90, 64), 1, torch.float16).to(dev)
+    both = H.abi_quant(q, k, None, "HND", 0.125)
+    only_q = H.abi_quant(q, k[:, :, :0], None, "HND", 0.125)
+    only_k = H.abi_quant(q[:, :, :0], k, None, "HND", 0.125)
+    assert torch.equal(only_q[0], both[0]) and torch.equal(only_q[1], both[1])
+    assert torch.equal(only_k[2], both[2]) and torch.equal(only_k[3], both[3])
