@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SAGE_ABI_VERSION 2
+#define SAGE_ABI_VERSION 3
 
 #define SAGE_DTYPE_F16 0
 #define SAGE_DTYPE_BF16 1
@@ -97,6 +97,24 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
                                  const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
                                  int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* stream);
 
+/* Persistent scheduling for problems that do not fill the GPU evenly.
+ * No counterpart in the reference.  sage_qk_int8_sv_f16_attn gives every thread block one whole
+ * 128-row query tile; a B200 runs 296 of them at a time, so 320 tiles (B=1, H=10, S=4096) take two
+ * rounds.  Given a workspace, the _ws entry points cut the work into 296 equal spans of KV-tile
+ * steps instead, keep partial results (fp32) in the workspace and merge them with a second small
+ * kernel; they fall back to the plain launch when that would not pay, when the workspace is NULL
+ * or too small, or when s_dump is set.  Results agree with the plain launch to fp32 rounding of
+ * the merge (same int8 products, same softmax).
+ * sage_attn_workspace_bytes: bytes the _ws calls want for this problem on the current device, 0 if
+ * they would use the plain launch anyway.  The workspace needs no initialisation and may be
+ * reused by the next call on the same stream. */
+int64_t sage_attn_workspace_bytes(int B, int Hq, int Sq, int Skv, int D, int is_causal);
+int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                                int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                                const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                                int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* workspace,
+                                int64_t workspace_bytes, void* stream);
+
 /* Un-quantised attention for short sequences: O = softmax2(sm_scale*log2(e) * Q K^T) V with Q and K
  * in fp16 or bf16 as the caller holds them.
  * Replaces fp16_attn_gfx11_t / bf16_attn_gfx11_t (csrc/attn_gfx11.h:21-39; csrc/attn_gfx11.cu:2275-2472,
@@ -111,6 +129,12 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
 int sage_direct_attn(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
                      int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
                      int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status, void* stream);
+
+/* sage_direct_attn with a workspace for persistent scheduling (see sage_attn_workspace_bytes). */
+int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                        int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
+                        int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status,
+                        void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Smooth-K quantisation for callers that must not allocate device memory.
  * No counterpart in the reference (its launchers allocate through torch).

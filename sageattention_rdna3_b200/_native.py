@@ -68,6 +68,14 @@ def load_abi() -> ctypes.CDLL:
     lib.sage_qk_int8_sv_f16_attn_lse.restype = i
     lib.sage_qk_int8_sv_f16_attn_lse.argtypes = [vp, vp, sp, vp, i64, i64, i64, vp, vp, i, i, i, i, i, i, i, i, vp, vp,
                                                  vp, vp]
+    lib.sage_attn_workspace_bytes.restype = i64
+    lib.sage_attn_workspace_bytes.argtypes = [i, i, i, i, i, i]
+    lib.sage_qk_int8_sv_f16_attn_ws.restype = i
+    lib.sage_qk_int8_sv_f16_attn_ws.argtypes = [vp, vp, sp, vp, i64, i64, i64, vp, vp, i, i, i, i, i, i, i, i, vp, vp,
+                                                vp, vp, i64, vp]
+    lib.sage_direct_attn_ws.restype = i
+    lib.sage_direct_attn_ws.argtypes = [sp, sp, sp, vp, i64, i64, i64, i, i, i, i, i, i, i, i, ctypes.c_float, vp, vp,
+                                        vp, i64, vp]
     lib.sage_direct_attn.restype = i
     lib.sage_direct_attn.argtypes = [sp, sp, sp, vp, i64, i64, i64, i, i, i, i, i, i, i, i, ctypes.c_float, vp, vp, vp]
     _abi = lib

@@ -33,12 +33,14 @@ def _status_word(device: torch.device) -> torch.Tensor:
     return word
 
 
-def check_status(device: Union[torch.device, int, None] = None) -> None:
+def check_status(device: Union[torch.device, int, str, None] = None) -> None:
     """Synchronise and raise if a kernel on ``device`` reported an internal error since the last check."""
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
     elif isinstance(device, int):
         device = torch.device("cuda", device)
+    elif isinstance(device, str):
+        device = torch.device(device)
     word = _status_word(device)
     code = int(word.item())
     if code != 0:

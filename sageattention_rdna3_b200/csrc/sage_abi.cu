@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -157,21 +158,140 @@ void fill_attn_params(sage::AttnParams* pp, void* o, int64_t o_stride_b, int64_t
   p.test_drop_v_load = (getenv("SAGE_TEST_DROP_V_LOAD") != nullptr) ? 1 : 0;
 }
 
+int sm_count(int* out) {
+  static int cached[64] = {};
+  int dev = 0;
+  SAGE_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) {
+    *out = cached[dev];
+    return SAGE_OK;
+  }
+  int sms = 0;
+  SAGE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (dev >= 0 && dev < 64) cached[dev] = sms;
+  *out = sms;
+  return SAGE_OK;
+}
+
+// Persistent ("stream-K") scheduling.  The plain launch gives every CTA one whole item (a 128-row
+// query tile with all of its KV tiles); with two CTAs per SM that fills the GPU in waves of
+// 2 * SMs items, and a problem of 320 items (B=1, H=10, S=4096) takes two waves where 1.08 would do.
+// The persistent launch cuts the T = sum of KV-tile steps into 2 * SMs equal spans instead; a span
+// that covers part of an item leaves a partial result in the workspace and a merge kernel combines
+// them.  It costs about three KV-tile steps per CTA (a second pipeline fill and drain, the merge), so
+// it is used when the estimate says it saves at least 8 %.
+struct StreamKPlan {
+  bool use = false;
+  int grid = 0;
+  int nkv_full = 0;
+  int tiles_per_head = 0;
+  long long total_tiles = 0;
+  size_t workspace_bytes = 0;
+};
+
+int plan_streamk(StreamKPlan* plan, int B, int Hq, int Sq, int Skv, int D, int is_causal) {
+  *plan = StreamKPlan();
+  if (Sq <= 0 || Skv <= 0) return SAGE_OK;
+  if (const char* e = getenv("SAGE_STREAMK")) {
+    if (e[0] == '0') return SAGE_OK;                    // SAGE_STREAMK=0 turns the persistent launch off, =1 forces it
+  }
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc) return rc;
+  const long long slots = 2LL * sms;
+  const long long nq = (Sq + sage::kBlockM - 1) / sage::kBlockM;
+  const long long nkv = (Skv + sage::kBlockN - 1) / sage::kBlockN;
+  long long per_head;
+  if (!is_causal) per_head = nq * nkv;
+  else if (nq <= nkv) per_head = nq * (nq + 1) / 2;
+  else per_head = nkv * (nkv + 1) / 2 + (nq - nkv) * nkv;
+  const long long items = nq * B * Hq;
+  const long long total = per_head * B * Hq;
+  if (per_head > 0x7fffffffLL || items > 0x7fffffffLL) return SAGE_OK;
+  const long long grid = total < slots ? total : slots;
+  // Makespans in KV-tile steps of a CTA that shares its SM with another one.  Plain launch: full
+  // waves of `slots` items, then a tail wave that runs about 1.4x faster per CTA if it leaves every
+  // CTA alone on its SM; under a causal mask the heavy-first order packs items almost evenly.  About
+  // 3 steps of fixed cost per wave (set-up, pipeline fill and drain, epilogue).  Persistent launch:
+  // T / G steps, the same fixed cost once, two more pipeline restarts at item boundaries, and the
+  // merge (about 5 us plus its traffic at 4 TB/s; one step is about 1.95 us).
+  double plain;
+  if (is_causal) {
+    plain = std::max<double>(static_cast<double>(std::min(nq, nkv)), 1.03 * total / slots) + 3.0;
+  } else {
+    const long long full = items / slots, tail = items % slots;
+    plain = static_cast<double>(full) * (nkv + 3.0);
+    if (tail > 0) plain += (tail <= sms ? 0.72 : 1.0) * nkv + 3.0;
+  }
+  const double merge_mb = (static_cast<double>(grid) * 2 * sage::kBlockM * D * 4 +
+                           static_cast<double>(std::min<long long>(items, 2 * grid)) * sage::kBlockM * D * 2) / 1e6;
+  const double merge_steps = (5.0 + merge_mb / 4.0) / 1.95;
+  const double persistent = static_cast<double>(total) / grid + 5.0 + merge_steps;
+  bool use = persistent < 0.95 * plain;
+  if (const char* e = getenv("SAGE_STREAMK")) use = (e[0] == '1') || use;
+  if (!use) return SAGE_OK;
+  plan->use = true;
+  plan->grid = static_cast<int>(grid);
+  plan->nkv_full = static_cast<int>(nkv);
+  plan->tiles_per_head = static_cast<int>(per_head);
+  plan->total_tiles = total;
+  plan->workspace_bytes = static_cast<size_t>(grid) * 2 * sage::kBlockM * (D + 1) * sizeof(float);
+  return SAGE_OK;
+}
+
+template <typename Kernel>
+int configure_smem(Kernel kern, int smem_bytes, bool* configured) {
+  int dev = 0;
+  SAGE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    SAGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  return SAGE_OK;
+}
+
 template <int D, bool CAUSAL, bool DUMP, bool QKF = false, int KST = 0>
 int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
                 const sage::AttnParams& p, cudaStream_t stream) {
   auto kern = sage::sage_attn_kernel<D, CAUSAL, DUMP, QKF, KST>;
   constexpr int kSmem = sage::AttnSmem<D, QKF ? 2 : 1, KST>::kTotal;
   static bool configured[64] = {};
-  int dev = 0;
-  SAGE_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    SAGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  int rc = configure_smem(kern, kSmem, configured);
+  if (rc) return rc;
   const long long grid = static_cast<long long>(p.n_q_tiles) * p.B * p.Hq;
   if (grid > 0x7fffffffLL) return fail(SAGE_ERR_INVALID, "too many query tiles for one launch (%lld)", grid);
   kern<<<static_cast<unsigned>(grid), sage::kAttnThreads, kSmem, stream>>>(tq, tk, tv, to, p);
+  SAGE_CUDA(cudaGetLastError());
+  return SAGE_OK;
+}
+
+// The persistent launch and its merge.  `workspace` holds the partial results:
+// [grid][2][128][D] fp32 outputs, then [grid][2][128] fp32 log-sum-exps.
+template <int D, bool CAUSAL, bool QKF>
+int launch_attn_streamk(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+                        sage::AttnParams p, const StreamKPlan& plan, void* workspace, cudaStream_t stream) {
+  auto kern = sage::sage_attn_kernel<D, CAUSAL, false, QKF, 0, true>;
+  constexpr int kSmem = sage::AttnSmem<D, QKF ? 2 : 1, 0>::kTotal;
+  static bool configured[64] = {};
+  int rc = configure_smem(kern, kSmem, configured);
+  if (rc) return rc;
+  p.sk_total_tiles = plan.total_tiles;
+  p.sk_tiles_per_head = plan.tiles_per_head;
+  p.sk_nkv_full = plan.nkv_full;
+  p.part_o = static_cast<float*>(workspace);
+  p.part_lse = p.part_o + static_cast<size_t>(plan.grid) * 2 * sage::kBlockM * D;
+  kern<<<static_cast<unsigned>(plan.grid), sage::kAttnThreads, kSmem, stream>>>(tq, tk, tv, to, p);
+  SAGE_CUDA(cudaGetLastError());
+  sage::MergeParams m;
+  m.part_o = p.part_o; m.part_lse = p.part_lse;
+  m.o = p.o; m.o_stride_b = p.o_stride_b; m.o_stride_h = p.o_stride_h; m.o_stride_s = p.o_stride_s;
+  m.lse = p.lse;
+  m.Hq = p.Hq; m.Sq = p.Sq; m.n_q_tiles = p.n_q_tiles;
+  m.nkv_full = plan.nkv_full; m.tiles_per_head = plan.tiles_per_head; m.total_tiles = plan.total_tiles;
+  m.attn_grid = plan.grid;
+  m.causal = CAUSAL ? 1 : 0; m.out_bf16 = p.out_bf16;
+  const long long items = static_cast<long long>(p.n_q_tiles) * p.B * p.Hq;
+  sage::sage_attn_merge_kernel<D><<<static_cast<unsigned>(items * sage::kMergeSplit), 256, 0, stream>>>(m);
   SAGE_CUDA(cudaGetLastError());
   return SAGE_OK;
 }
@@ -313,6 +433,23 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
                                  int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
                                  const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
                                  int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* stream) {
+  return sage_qk_int8_sv_f16_attn_ws(q_i8, k_i8, v16, o, o_stride_b, o_stride_h, o_stride_s, q_scale, k_scale,
+                                     out_dtype, B, Hq, Hkv, Sq, Skv, D, is_causal, lse, s_dump, status, nullptr, 0,
+                                     stream);
+}
+
+int64_t sage_attn_workspace_bytes(int B, int Hq, int Sq, int Skv, int D, int is_causal) {
+  StreamKPlan plan;
+  if (B <= 0 || Hq <= 0 || (D != 64 && D != 128)) return 0;
+  if (plan_streamk(&plan, B, Hq, Sq, Skv, D, is_causal) != SAGE_OK) return 0;
+  return plan.use ? static_cast<int64_t>(plan.workspace_bytes) : 0;
+}
+
+int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                                int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                                const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                                int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* workspace,
+                                int64_t workspace_bytes, void* stream) {
   SAGE_REQUIRE(q_i8 && v16 && o && q_scale, "sage_qk_int8_sv_f16_attn: null pointer");
   SAGE_REQUIRE(Skv == 0 || (k_i8 && v16->ptr && k_scale), "sage_qk_int8_sv_f16_attn: null pointer");
   SAGE_REQUIRE(out_dtype == SAGE_DTYPE_F16 || out_dtype == SAGE_DTYPE_BF16,
@@ -366,6 +503,20 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
     if (rc) return rc;
   }
   const bool dump = (s_dump != nullptr);
+  if (workspace != nullptr && !dump) {
+    StreamKPlan plan;
+    int rc = plan_streamk(&plan, B, Hq, Sq, Skv, D, is_causal);
+    if (rc) return rc;
+    if (plan.use && static_cast<size_t>(workspace_bytes) >= plan.workspace_bytes) {
+      SAGE_REQUIRE(aligned16(workspace), "sage_qk_int8_sv_f16_attn_ws: workspace must be 16-byte aligned");
+      if (D == 128) {
+        return is_causal ? launch_attn_streamk<128, true, false>(tq, tk, tv, to, p, plan, workspace, st)
+                         : launch_attn_streamk<128, false, false>(tq, tk, tv, to, p, plan, workspace, st);
+      }
+      return is_causal ? launch_attn_streamk<64, true, false>(tq, tk, tv, to, p, plan, workspace, st)
+                       : launch_attn_streamk<64, false, false>(tq, tk, tv, to, p, plan, workspace, st);
+    }
+  }
 #define SAGE_LAUNCH(DD, CC)                                                     \
   (dump ? launch_attn<DD, CC, true>(tq, tk, tv, to, p, st) : launch_attn<DD, CC, false>(tq, tk, tv, to, p, st))
   if (D == 128) return is_causal ? SAGE_LAUNCH(128, true) : SAGE_LAUNCH(128, false);
@@ -376,6 +527,14 @@ int sage_qk_int8_sv_f16_attn_lse(const int8_t* q_i8, const int8_t* k_i8, const s
 int sage_direct_attn(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
                      int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
                      int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status, void* stream) {
+  return sage_direct_attn_ws(q, k, v16, o, o_stride_b, o_stride_h, o_stride_s, dtype, B, Hq, Hkv, Sq, Skv, D, is_causal,
+                             sm_scale, lse, status, nullptr, 0, stream);
+}
+
+int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                        int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
+                        int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status,
+                        void* workspace, int64_t workspace_bytes, void* stream) {
   SAGE_REQUIRE(q && q->ptr && v16 && o, "sage_direct_attn: null pointer");
   SAGE_REQUIRE(Skv == 0 || (k && k->ptr && v16->ptr), "sage_direct_attn: null pointer");
   SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_direct_attn: dtype must be f16 or bf16");
@@ -413,11 +572,25 @@ int sage_direct_attn(const sage_strided_t* q, const sage_strided_t* k, const sag
   if (rc) return rc;
   rc = encode_strided_16bit(&to, qk_dt, o, D, Sq, Hq, B, o_stride_s, o_stride_h, o_stride_b, 32, "o");
   if (rc) return rc;
+  if (workspace != nullptr) {
+    StreamKPlan plan;
+    rc = plan_streamk(&plan, B, Hq, Sq, Skv, D, is_causal);
+    if (rc) return rc;
+    if (plan.use && static_cast<size_t>(workspace_bytes) >= plan.workspace_bytes) {
+      SAGE_REQUIRE(aligned16(workspace), "sage_direct_attn_ws: workspace must be 16-byte aligned");
+      if (D == 128) {
+        return is_causal ? launch_attn_streamk<128, true, true>(tq, tk, tv, to, p, plan, workspace, st)
+                         : launch_attn_streamk<128, false, true>(tq, tk, tv, to, p, plan, workspace, st);
+      }
+      return is_causal ? launch_attn_streamk<64, true, true>(tq, tk, tv, to, p, plan, workspace, st)
+                       : launch_attn_streamk<64, false, true>(tq, tk, tv, to, p, plan, workspace, st);
+    }
+  }
   if (D == 128) {
     // A grid that cannot put two CTAs on every SM anyway takes the deeper K/V rings (one CTA per SM).
-    int dev = 0, sms = 0;
-    SAGE_CUDA(cudaGetDevice(&dev));
-    SAGE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    rc = sm_count(&sms);
+    if (rc) return rc;
     const long long ctas = static_cast<long long>(p.n_q_tiles) * B * Hq;
     if (ctas <= sms) {
       return is_causal ? launch_attn<128, true, false, true, 2>(tq, tk, tv, to, p, st)

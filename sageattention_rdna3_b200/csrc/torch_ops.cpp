@@ -199,11 +199,15 @@ at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, c
   c10::cuda::CUDAGuard guard(q_i8.device());
   const sage_strided_t vs = strided_of(v, value_layout);
   const sage_strided_t os = strided_of(o, layout);
-  check_rc(sage_qk_int8_sv_f16_attn_lse(q_i8.data_ptr<int8_t>(), k_i8.data_ptr<int8_t>(), &vs, o.data_ptr(), os.stride_b,
-                                        os.stride_h, os.stride_s, q_scale.data_ptr<float>(),
-                                        k_scale.data_ptr<float>(), dtype_code(o), (int)B, (int)Hq, (int)Hkv, (int)Sq,
-                                        (int)Skv, (int)D, (int)is_causal, lse_ptr, dump_ptr, status_ptr,
-                                        current_stream(q_i8)),
+  // Problems that would fill the GPU unevenly run on persistent CTAs and need scratch for partial results.
+  at::Tensor workspace;
+  const int64_t ws_bytes = dump_ptr ? 0 : sage_attn_workspace_bytes((int)B, (int)Hq, (int)Sq, (int)Skv, (int)D, (int)is_causal);
+  if (ws_bytes > 0) workspace = at::empty({ws_bytes}, q_i8.options().dtype(at::kByte));
+  check_rc(sage_qk_int8_sv_f16_attn_ws(q_i8.data_ptr<int8_t>(), k_i8.data_ptr<int8_t>(), &vs, o.data_ptr(), os.stride_b,
+                                       os.stride_h, os.stride_s, q_scale.data_ptr<float>(),
+                                       k_scale.data_ptr<float>(), dtype_code(o), (int)B, (int)Hq, (int)Hkv, (int)Sq,
+                                       (int)Skv, (int)D, (int)is_causal, lse_ptr, dump_ptr, status_ptr,
+                                       ws_bytes > 0 ? workspace.data_ptr() : nullptr, ws_bytes, current_stream(q_i8)),
            "qk_int8_sv_f16_attn");
   return o;
 }
@@ -246,9 +250,13 @@ at::Tensor direct_attn(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   c10::cuda::CUDAGuard guard(q.device());
   const sage_strided_t qs = strided_of(q, layout), ks = strided_of(k, layout), vs = strided_of(v, value_layout);
   const sage_strided_t os = strided_of(o, layout);
-  check_rc(sage_direct_attn(&qs, &ks, &vs, o.data_ptr(), os.stride_b, os.stride_h, os.stride_s, dtype_code(q), (int)dq.B,
-                            (int)dq.H, (int)dk.H, (int)dq.S, (int)dk.S, (int)dq.D, (int)is_causal, (float)sm_scale,
-                            lse_ptr, status_ptr, current_stream(q)),
+  at::Tensor workspace;
+  const int64_t ws_bytes = sage_attn_workspace_bytes((int)dq.B, (int)dq.H, (int)dq.S, (int)dk.S, (int)dq.D, (int)is_causal);
+  if (ws_bytes > 0) workspace = at::empty({ws_bytes}, q.options().dtype(at::kByte));
+  check_rc(sage_direct_attn_ws(&qs, &ks, &vs, o.data_ptr(), os.stride_b, os.stride_h, os.stride_s, dtype_code(q),
+                               (int)dq.B, (int)dq.H, (int)dk.H, (int)dq.S, (int)dk.S, (int)dq.D, (int)is_causal,
+                               (float)sm_scale, lse_ptr, status_ptr, ws_bytes > 0 ? workspace.data_ptr() : nullptr,
+                               ws_bytes, current_stream(q)),
            name);
   return o;
 }

@@ -23,7 +23,8 @@ def declared_symbols():
 def test_header_declares_the_expected_entry_points():
     assert declared_symbols() == sorted(["sage_abi_version", "sage_last_error", "sage_mean_seq",
                                          "sage_quant_qk_int8", "sage_v_to_f16", "sage_qk_int8_sv_f16_attn",
-                                         "sage_qk_int8_sv_f16_attn_lse", "sage_direct_attn",
+                                         "sage_qk_int8_sv_f16_attn_lse", "sage_direct_attn", "sage_attn_workspace_bytes",
+                                         "sage_qk_int8_sv_f16_attn_ws", "sage_direct_attn_ws",
                                          "sage_quant_qk_int8_smooth_static"])
 
 

@@ -202,7 +202,7 @@ def test_gpu_matches_golden_fixtures(dev, name):
 # BASELINE sizes.  The oracle cannot do the whole of configs 3-5 in seconds, so: (a) full-size
 # launches are checked through size-independent properties, (b) whole (batch, kv-head) units or row
 # blocks of them are compared with the oracle.
-def test_config3_full_size_properties_and_sampled_units(dev):
+def test_config3_full_size_properties_and_sampled_units(dev, monkeypatch):
     """B=2 H=32 S=8192 D=128 bf16 HND causal smooth_k, K with a per-channel DC offset."""
     B, Hh, S, D = 2, 32, 8192, 128
     g = torch.Generator(device="cpu").manual_seed(0)
@@ -222,9 +222,16 @@ def test_config3_full_size_properties_and_sampled_units(dev):
     # (3) linear in V, exactly: doubling V doubles every product, sum and the rounded result
     o2 = sageattn(qd, kd, vd * 2, **kw)
     assert torch.equal(o2, o * 2)
-    # (4) units are independent: one (batch, head) computed alone equals its slice, bit for bit
-    alone = sageattn(qd[1:2, 5:6].contiguous(), kd[1:2, 5:6].contiguous(), vd[1:2, 5:6].contiguous(), **kw)
+    # (4) units are independent: one (batch, head) computed alone equals its slice, bit for bit when
+    # both run the one-tile-per-CTA launch; a single head would by default run on persistent CTAs,
+    # whose fp32 merge of partial results rounds differently in the last bit
+    unit = (qd[1:2, 5:6].contiguous(), kd[1:2, 5:6].contiguous(), vd[1:2, 5:6].contiguous())
+    monkeypatch.setenv("SAGE_STREAMK", "0")
+    alone = sageattn(*unit, **kw)
+    monkeypatch.delenv("SAGE_STREAMK")
     assert torch.equal(alone, o[1:2, 5:6])
+    acc = so.accuracy(sageattn(*unit, **kw).float().cpu(), alone.float().cpu())
+    assert acc["cos"] >= 0.999999 and acc["max_abs"] <= 2 ** -6, acc
     check_status(dev)
     # (5) two whole units against the oracle
     for (b, h) in ((0, 0), (1, 31)):
@@ -540,3 +547,52 @@ def test_one_sided_quantisation_through_the_c_abi(dev):
     only_k = H.abi_quant(q[:, :, :0], k, None, "HND", 0.125)
     assert torch.equal(only_q[0], both[0]) and torch.equal(only_q[1], both[1])
     assert torch.equal(only_k[2], both[2]) and torch.equal(only_k[3], both[3])
+
+
+# ----------------------------------------------------------------------------------------------
+# Persistent ("stream-K") launch: spans of KV-tile steps per CTA, partial results merged.  Forced
+# here on shapes of every kind, compared with the one-tile-per-CTA launch (same int8 products and
+# softmax; the merge adds fp32 roundings) and with the oracle.
+STREAMK_CASES = [
+    # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth_k, kernel
+    (1, 10, 10, 4096, 4096, 64, torch.float16, "NHD", False, False, "int8"),    # BASELINE config 2: 320 items
+    (2, 32, 32, 2048, 2048, 128, torch.bfloat16, "HND", True, True, "int8"),    # many short causal items per CTA
+    (1, 4, 1, 1000, 1000, 128, torch.bfloat16, "HND", True, False, "int8"),     # GQA, ragged
+    (1, 3, 3, 4096, 4096, 128, torch.bfloat16, "NHD", False, False, "int8"),    # few heads (VAE shapes)
+    (2, 4, 2, 300, 333, 128, torch.bfloat16, "NHD", False, True, "int8"),
+    (1, 2, 2, 130, 2048, 64, torch.float16, "HND", True, False, "int8"),        # Sq < Skv, causal
+    (1, 2, 2, 2048, 300, 64, torch.float16, "HND", True, False, "int8"),        # Sq > Skv, causal
+    (1, 20, 20, 1024, 1024, 64, torch.float16, "NHD", False, False, "direct"),
+    (1, 16, 16, 2048, 512, 128, torch.bfloat16, "HND", False, False, "direct"),
+    (1, 5, 5, 640, 640, 128, torch.float16, "HND", True, False, "direct"),
+    (1, 1, 1, 128, 128, 64, torch.float16, "HND", False, False, "int8"),        # one step in all
+]
+
+
+@pytest.mark.parametrize("case", STREAMK_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_persistent_launch_matches_plain_launch_and_oracle(dev, monkeypatch, case):
+    from sageattention_rdna3_b200 import check_status, sageattn
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth, kernel = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype, offset=1.0 if smooth else 0.0)
+    # V far from 1 and of both signs, so that stale or foreign data in the output cannot pass for a result
+    v = (H.randn(sk, 2, torch.float32) * 3.0 + 0.5).to(dtype)
+    kw = dict(tensor_layout=layout, is_causal=causal, smooth_k=smooth, kernel=kernel, return_lse=True)
+    monkeypatch.setenv("SAGE_STREAMK", "0")
+    o_plain, lse_plain = sageattn(q.to(dev), k.to(dev), v.to(dev), **kw)
+    monkeypatch.setenv("SAGE_STREAMK", "1")
+    # poison what the allocator will hand out as workspace
+    junk = torch.full((64 << 20,), float("nan"), dtype=torch.float32, device=dev)
+    del junk
+    o_sk, lse_sk = sageattn(q.to(dev), k.to(dev), v.to(dev), **kw)
+    check_status(dev)
+    assert torch.isfinite(o_sk.float()).all()
+    acc = so.accuracy(o_sk.float().cpu(), o_plain.float().cpu())
+    assert acc["cos"] >= 0.999999 and acc["max_abs"] <= (2 ** -5 if dtype == torch.bfloat16 else 2 ** -8), acc
+    assert (lse_sk - lse_plain).abs().max().item() < 1e-4
+    if kernel == "int8":
+        emu = so.sageattn_emulated(q, k, v, tensor_layout=layout, is_causal=causal, smooth_k=smooth)
+    else:
+        emu = so.direct_attn_emulated(q, k, v, tensor_layout=layout, is_causal=causal)
+    acc2 = so.accuracy(o_sk.float().cpu(), emu.float())
+    assert acc2["cos"] >= COS_MIN and acc2["rel_l1"] <= REL_L1_MAX, acc2
