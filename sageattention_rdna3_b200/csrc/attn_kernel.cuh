@@ -1,19 +1,25 @@
-// Fused INT8 attention for sm_100a: replaces attn_kernel_impl_t / attn_kernel_impl_32_t and the
-// WMMA helpers of the reference (csrc/attn_gfx11.cu:409-1243, csrc/mma_gfx11.h).
+// Fused attention for sm_100a: replaces attn_kernel_impl_t / attn_kernel_impl_32_t, the un-quantised
+// direct_attn_kernel_impl_t and the WMMA helpers of the reference (csrc/attn_gfx11.cu:409-1243,
+// :1468-1846, csrc/mma_gfx11.h).
 //
-// One CTA owns one 128-row query tile of one (batch, query head) and streams the KV sequence in
+// A CTA works on 128-row query tiles of one (batch, query head) and streams the KV sequence in
 // 128-row tiles:
-//   warp 4   : TMA producer   - Q once, then K (int8) and V (fp16) tiles into a shared-memory ring
-//   warp 5   : MMA issuer     - S = Q.K^T  (tcgen05.mma kind::i8, int32 accumulator in TMEM),
+//   warp 4   : TMA producer   - Q, then K (int8, or fp16 / bf16 in the un-quantised variant) and
+//                               V (fp16) tiles into a shared-memory ring
+//   warp 5   : MMA issuer     - S = Q.K^T  (tcgen05.mma kind::i8, int32 accumulator in TMEM; kind::f16
+//                               with an fp32 accumulator in the un-quantised variant),
 //                               O += P.V   (tcgen05.mma kind::f16, P read from TMEM, fp32 accumulator)
 //   warps 0-3: softmax        - thread t owns query row t: tcgen05.ld of S, dequantise with
-//                               q_scale[row/32]*k_scale[col/16], causal / length mask, base-2 online
-//                               softmax in fp32, P rounded to fp16 and written back into TMEM over S,
-//                               lazy rescale of O, final normalisation and store.
+//                               q_scale[row/32]*k_scale[col/16] (or scale by sm_scale*log2e), causal /
+//                               length mask, base-2 online softmax in fp32, P rounded to fp16 and
+//                               written back into TMEM over S, lazy rescale of O, final
+//                               normalisation and store (optionally the log-sum-exp).
 // Two CTAs fit on one SM (112 KB of shared memory and 256 TMEM columns each), so the tensor pipe of
 // one overlaps the softmax of the other.
+// Launch shapes: one CTA per query tile (plain), or 2 * SMs persistent CTAs that each work through an
+// equal span of KV-tile steps and leave partial results for sage_attn_merge_kernel (STREAMK).
 //
-// TMEM columns: [0,128) S as int32, reused in place as P (fp16 pairs in columns [0,64));
+// TMEM columns: [0,128) S as int32 / fp32, reused in place as P (fp16 pairs in columns [0,64));
 //               [128,128+D) O as fp32.
 // Numerics follow csrc/attn_gfx11.cu:487-502,608-689,769-786: exact int32 scores, fp32 softmax in
 // base 2 with the row sum taken before P is rounded, P in fp16, V in fp16, fp32 accumulation, one

@@ -1,5 +1,7 @@
 """Two ranks on two GPUs (NCCL): each computes its (batch, kv-head) units with the CUDA kernels,
-the all-gather must reproduce the single-GPU result bit for bit.  Skipped with fewer than 2 GPUs."""
+the all-gather must reproduce the single-GPU result - bit for bit with the one-tile-per-CTA launch
+(SAGE_STREAMK=0), to fp32 rounding of the merge when the scheduler may pick persistent CTAs (a rank
+with half of the units cuts its work into different spans).  Skipped with fewer than 2 GPUs."""
 import os
 import socket
 import sys
@@ -27,8 +29,10 @@ def _inputs(layout):
     return randn(shp(Hq), 0, torch.bfloat16), randn(shp(Hkv), 1, torch.bfloat16, offset=1.0), randn(shp(Hkv), 2, torch.bfloat16)
 
 
-def _worker(rank, world, port, layout, out_dir):
+def _worker(rank, world, port, layout, streamk, out_dir):
     sys.path.insert(0, ROOT)
+    if streamk is not None:
+        os.environ["SAGE_STREAMK"] = streamk
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -45,14 +49,20 @@ def _worker(rank, world, port, layout, out_dir):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("streamk", ["0", None])
 @pytest.mark.parametrize("layout", ["HND", "NHD"])
-def test_two_gpus_reproduce_one(tmp_path, layout):
+def test_two_gpus_reproduce_one(tmp_path, monkeypatch, layout, streamk):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    mp.spawn(_worker, args=(2, _free_port(), layout, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), layout, streamk, str(tmp_path)), nprocs=2, join=True)
     from sageattention_rdna3_b200 import sageattn
+    if streamk is not None:
+        monkeypatch.setenv("SAGE_STREAMK", streamk)
     q, k, v = (t.cuda(0) for t in _inputs(layout))
     want = sageattn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True).cpu()
     for r in range(2):
         got = torch.load(os.path.join(str(tmp_path), f"rank{r}.pt"))
-        assert torch.equal(got, want), f"rank {r}"
+        if streamk == "0":
+            assert torch.equal(got, want), f"rank {r}"
+        else:
+            assert (got.float() - want.float()).abs().max().item() <= 2 ** -5, f"rank {r}"
