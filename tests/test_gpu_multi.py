@@ -66,3 +66,53 @@ def test_two_gpus_reproduce_one(tmp_path, monkeypatch, layout, streamk):
             assert torch.equal(got, want), f"rank {r}"
         else:
             assert (got.float() - want.float()).abs().max().item() <= 2 ** -5, f"rank {r}"
+
+
+def _cp_worker(rank, world, port, layout, causal, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from sageattention_rdna3_b200 import check_status
+        from sageattention_rdna3_b200.context_parallel import sageattn_context_parallel
+        s_dim = 2 if layout == "HND" else 1
+        q, k, v = (t.chunk(world, dim=s_dim)[rank].contiguous().cuda(rank) for t in _cp_inputs(layout))
+        out = sageattn_context_parallel(q, k, v, tensor_layout=layout, is_causal=causal, smooth_k=True, kernel="int8")
+        check_status(rank)
+        torch.save(out.cpu(), os.path.join(out_dir, f"cp{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _cp_inputs(layout):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import randn
+    B, Hq, Hkv, S, D = 1, 4, 2, 2048, 128
+    shp = (lambda h: (B, h, S, D)) if layout == "HND" else (lambda h: (B, S, h, D))
+    return randn(shp(Hq), 0, torch.bfloat16), randn(shp(Hkv), 1, torch.bfloat16, offset=1.0), randn(shp(Hkv), 2, torch.bfloat16)
+
+
+@pytest.mark.parametrize("layout,causal", [("HND", True), ("NHD", False)])
+def test_context_parallel_ring_on_two_gpus(tmp_path, layout, causal):
+    """Sequence shards on two GPUs, KV passed round the ring over NCCL, partials merged with the
+    kernel's log-sum-exp: equal to one-GPU attention to the accuracy of the INT8 path."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_cp_worker, args=(2, _free_port(), layout, causal, str(tmp_path)), nprocs=2, join=True)
+    sys.path.insert(0, ROOT)
+    from oracle import sage_oracle as so
+    from sageattention_rdna3_b200 import sageattn
+    q, k, v = _cp_inputs(layout)
+    want = sageattn(q.cuda(0), k.cuda(0), v.cuda(0), tensor_layout=layout, is_causal=causal, smooth_k=True,
+                    kernel="int8").cpu()
+    s_dim = 2 if layout == "HND" else 1
+    got = torch.cat([torch.load(os.path.join(str(tmp_path), f"cp{r}.pt")) for r in range(2)], dim=s_dim)
+    acc = so.accuracy(got.float(), want.float())
+    # two INT8 runs with different quantisation groups and K means: each is ~1.1e-2 (rel L1) from fp32
+    assert acc["cos"] >= 0.9999 and acc["rel_l1"] <= 2e-2, acc
+    ref = so.sdpa_fp32(q, k, v, tensor_layout=layout, is_causal=causal)
+    acc2 = so.accuracy(got.float(), ref)
+    assert acc2["cos"] > 0.98 and acc2["max_abs"] < 0.35, acc2
