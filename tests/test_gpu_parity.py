@@ -604,3 +604,24 @@ def test_persistent_launch_matches_plain_launch_and_oracle(dev, monkeypatch, cas
         emu = so.direct_attn_emulated(q, k, v, tensor_layout=layout, is_causal=causal)
     acc2 = so.accuracy(o_sk.float().cpu(), emu.float())
     assert acc2["cos"] >= COS_MIN and acc2["rel_l1"] <= REL_L1_MAX, acc2
+
+
+def test_scheduler_choices_for_known_shapes(dev, monkeypatch):
+    """sage_attn_workspace_bytes > 0 means the persistent launch will be used.  The choices below are
+    the measured ones: 320 items of 32 steps (BASELINE config 2) and the 4-head VAE shape gain from
+    it, one exact wave, two nearly full waves and the 4096-item config 3 do not."""
+    monkeypatch.delenv("SAGE_STREAMK", raising=False)
+    lib = H._native.load_abi()
+    torch.cuda.set_device(dev)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    want = lambda B, Hq, Sq, Skv, D, causal: lib.sage_attn_workspace_bytes(B, Hq, Sq, Skv, D, causal)
+    assert want(1, 10, 4096, 4096, 64, 0) == 2 * sms * 2 * 128 * (64 + 1) * 4
+    assert want(1, 4, 16384, 16384, 128, 0) == 2 * sms * 2 * 128 * (128 + 1) * 4
+    assert want(1, 1, 8192, 8192, 128, 1) > 0                 # one causal head: 64 very unequal items
+    assert want(1, 2 * sms // 8, 1024, 4096, 128, 0) == 0     # exactly one wave of items
+    assert want(1, 16, 4096, 4096, 128, 0) == 0               # 512 items: the tail wave runs alone on its SMs
+    assert want(2, 32, 8192, 8192, 128, 1) == 0               # BASELINE config 3
+    assert want(1, 24, 32768, 32768, 128, 0) == 0             # BASELINE config 5
+    assert want(1, 2, 128, 0, 64, 0) == 0 and want(1, 2, 0, 128, 64, 0) == 0
+    monkeypatch.setenv("SAGE_STREAMK", "0")
+    assert want(1, 10, 4096, 4096, 64, 0) == 0
