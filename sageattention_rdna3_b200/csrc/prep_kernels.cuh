@@ -240,24 +240,39 @@ __global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepPa
   }
   blk -= p.k_blocks;
   // ---- V: 16-bit copy to fp16 [B,Hkv,Skv,D] (csrc/attn_gfx11.cu:377-381: __float2half_rn).
-  // Each thread converts four 16-byte vectors, 4096 bytes apart, so a warp moves 512 B per load.
+  // Each thread converts four 16-byte vectors, 4096 bytes apart in the output, so a warp moves 512 B
+  // per load; the four loads are issued before the first store.  (batch*head, position) of the
+  // first vector comes from one division, the others follow by stepping 256 / (D/8) rows.
   if (p.v16 == nullptr) return;
   constexpr int kVecPerRow = D / 8;
+  constexpr int kRowStep = kPrepThreads / kVecPerRow;
   const long long n_vec = static_cast<long long>(p.B) * p.Hkv * p.Skv * kVecPerRow;
   const long long base = static_cast<long long>(blk) * (kPrepThreads * 4) + threadIdx.x;
+  const int c = static_cast<int>(base % kVecPerRow) * 8;
+  const long long row0 = base / kVecPerRow;
+  int bh = static_cast<int>(row0 / p.Skv);
+  int s = static_cast<int>(row0 - static_cast<long long>(bh) * p.Skv);
+  uint4 raw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (base + static_cast<long long>(i) * kPrepThreads < n_vec) {
+      const int b = bh / p.Hkv, h = bh - b * p.Hkv;
+      const T* src = reinterpret_cast<const T*>(p.v.ptr) + b * p.v.stride_b + h * p.v.stride_h +
+                     static_cast<long long>(s) * p.v.stride_s + c;
+      raw[i] = __ldg(reinterpret_cast<const uint4*>(src));
+    }
+    s += kRowStep;
+    while (s >= p.Skv) {
+      s -= p.Skv;
+      ++bh;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const long long vec = base + static_cast<long long>(i) * kPrepThreads;
     if (vec < n_vec) {
-      const int c = static_cast<int>(vec % kVecPerRow) * 8;
-      const long long row = vec / kVecPerRow;
-      const int s = static_cast<int>(row % p.Skv);
-      const int bh = static_cast<int>(row / p.Skv);
-      const int b = bh / p.Hkv, h = bh % p.Hkv;
-      const T* src = reinterpret_cast<const T*>(p.v.ptr) + b * p.v.stride_b + h * p.v.stride_h +
-                     static_cast<long long>(s) * p.v.stride_s + c;
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
-      const T* xv = reinterpret_cast<const T*>(&raw);
+      const T* xv = reinterpret_cast<const T*>(&raw[i]);
       uint4 out;
       uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
