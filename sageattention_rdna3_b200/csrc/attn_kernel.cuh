@@ -129,6 +129,17 @@ __device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
 }
 constexpr int kHalfN = kBlockN / 2;      // the softmax works on 64-column halves of a KV tile
 
+// Two CTAs share an SM, and warp w of one shares a scheduler - and its exponential unit - with warp
+// w of the other.  Left alone, the two settle into a fixed relative phase, often one in which their
+// exponential passes coincide and both run at half speed.  Every second CTA to start on an SM
+// therefore yields (nanosleep 0) once per half-step: its period becomes a little longer, the relative
+// phase drifts through all values, and the pair sees the average overlap instead of the worst
+// (2-2.5 % on long sequences).  The counter is only ever read for its parity; it is never reset.
+#ifndef SAGE_DEPHASE
+#define SAGE_DEPHASE 1
+#endif
+static __device__ unsigned g_sm_arrivals[1024];
+
 // What one pass of the pipeline works on: KV tiles [kv_lo, kv_lo + n_kv) of one 128-row query tile
 // of one (batch, query head).  slot < 0: the pass covers every KV tile of the item and writes the
 // output; slot 0 / 1: it covers a part, and acc / l and m + log2 l go to that slot of the CTA's
@@ -522,6 +533,17 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
     constexpr bool kHintRole = SAGE_HINT_SOFTMAX;
+    bool yields = false;
+    if (SAGE_DEPHASE) {
+      volatile unsigned* arrival = reinterpret_cast<volatile unsigned*>(smem + L::kOffMisc + 12);
+      if (threadIdx.x == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        *arrival = atomicAdd(&g_sm_arrivals[smid & 1023u], 1u);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // the four softmax warps only
+      yields = (*arrival & 1u) != 0u;
+    }
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t t_o = tmem_base + lane_base + kColO;
     bool ok = true;
@@ -638,6 +660,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // tails) would pay for two exp passes on most steps otherwise.
       const bool attempt = !first_or_masked && !refused_last;
       if (attempt) {
+        if (yields) __nanosleep(0);
         const float sum = exp_pass(std::false_type{}, m_used);
         if (!__any_sync(0xffffffffu, !(sum <= kOptimisticSumMax))) {
           l += sum;
