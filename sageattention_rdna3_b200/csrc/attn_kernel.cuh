@@ -653,6 +653,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // the lazy-rescale rule would not have moved the maximum, P fits fp16 comfortably, and the
       // step is done without a pass over the scores for the maximum.  Otherwise (or if the sum is
       // not a number) fall through to the exact path and redo the step.
+      if (yields) __nanosleep(0);                       // see SAGE_DEPHASE
       bool done = false;
       float m_half = kMaskValue;
       const bool first_or_masked = (hh == 0) || masked;
@@ -660,7 +661,6 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // tails) would pay for two exp passes on most steps otherwise.
       const bool attempt = !first_or_masked && !refused_last;
       if (attempt) {
-        if (yields) __nanosleep(0);
         const float sum = exp_pass(std::false_type{}, m_used);
         if (!__any_sync(0xffffffffu, !(sum <= kOptimisticSumMax))) {
           l += sum;
