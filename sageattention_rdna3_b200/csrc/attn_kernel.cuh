@@ -534,7 +534,8 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // ------------------------------------------------------------------ softmax / epilogue
     constexpr bool kHintRole = SAGE_HINT_SOFTMAX;
     bool yields = false;
-    if (SAGE_DEPHASE) {
+    // (not in the persistent variant: its CTAs are given equal spans and must run at equal speed)
+    if (SAGE_DEPHASE && !STREAMK) {
       volatile unsigned* arrival = reinterpret_cast<volatile unsigned*>(smem + L::kOffMisc + 12);
       if (threadIdx.x == 0) {
         unsigned smid;

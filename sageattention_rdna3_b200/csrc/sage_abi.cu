@@ -213,7 +213,7 @@ int plan_streamk(StreamKPlan* plan, int B, int Hq, int Sq, int Skv, int D, int i
   // waves of `slots` items, then a tail wave that runs about 1.4x faster per CTA if it leaves every
   // CTA alone on its SM; under a causal mask the heavy-first order packs items almost evenly.  About
   // 3 steps of fixed cost per wave (set-up, pipeline fill and drain, epilogue).  Persistent launch:
-  // T / G steps, the same fixed cost once, two more pipeline restarts at item boundaries, and the
+  // 1.04 T / G steps, the same fixed cost once, two more pipeline restarts at item boundaries, and the
   // merge (about 5 us plus its traffic at 4 TB/s; one step is about 1.95 us).
   double plain;
   if (is_causal) {
@@ -226,7 +226,8 @@ int plan_streamk(StreamKPlan* plan, int B, int Hq, int Sq, int Skv, int D, int i
   const double merge_mb = (static_cast<double>(grid) * 2 * sage::kBlockM * D * 4 +
                            static_cast<double>(std::min<long long>(items, 2 * grid)) * sage::kBlockM * D * 2) / 1e6;
   const double merge_steps = (5.0 + merge_mb / 4.0) / 1.95;
-  const double persistent = static_cast<double>(total) / grid + 5.0 + merge_steps;
+  // (1.04: the persistent CTAs of an SM run in lock-step, without the de-phasing yield of the plain launch)
+  const double persistent = 1.04 * static_cast<double>(total) / grid + 5.0 + merge_steps;
   bool use = persistent < 0.95 * plain;
   if (const char* e = getenv("SAGE_STREAMK")) use = (e[0] == '1') || use;
   if (!use) return SAGE_OK;
