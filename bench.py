@@ -47,7 +47,7 @@ DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
 METRIC = "attention TOPS (4*B*H*S^2*D/t)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one sage_attn_kernel launch, from an ncu capture of
 # this workload (ncu --set full -k regex:sage_ on `bench.py --steps 1 --warmup 3`)
-ATTN_TRAFFIC_BYTES = {"C3": 376.7e6}
+ATTN_TRAFFIC_BYTES = {"C3": 379.3e6}
 
 
 def nominal_ops(w, B=None):
