@@ -625,3 +625,41 @@ def test_scheduler_choices_for_known_shapes(dev, monkeypatch):
     assert want(1, 2, 128, 0, 64, 0) == 0 and want(1, 2, 0, 128, 64, 0) == 0
     monkeypatch.setenv("SAGE_STREAMK", "0")
     assert want(1, 10, 4096, 4096, 64, 0) == 0
+
+
+# ----------------------------------------------------------------------------------------------
+# Seeded random sweep over small ragged shapes: both kernels, both launch schedules.
+def _sweep_cases(n=48):
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+    cases = []
+    for i in range(n):
+        hkv, rep = r(1, 3), (1, 2, 4)[r(0, 2)]
+        sq, skv = r(1, 700), r(1, 700)
+        if r(0, 3) == 0:
+            skv = sq                                    # self attention now and then
+        cases.append((r(1, 2), hkv * rep, hkv, sq, skv, (64, 128)[r(0, 1)], (torch.float16, torch.bfloat16)[r(0, 1)],
+                      ("HND", "NHD")[r(0, 1)], bool(r(0, 1)), bool(r(0, 1)), ("int8", "direct")[r(0, 1)], str(r(0, 1))))
+    return cases
+
+
+@pytest.mark.parametrize("case", _sweep_cases(), ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_random_ragged_shapes(dev, monkeypatch, case):
+    from sageattention_rdna3_b200 import check_status, sageattn
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth, kernel, streamk = case
+    monkeypatch.setenv("SAGE_STREAMK", streamk)
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype, offset=0.75 if smooth else 0.0)
+    v = (H.randn(sk, 2, torch.float32) * 2.0 - 0.25).to(dtype)
+    o, lse = sageattn(q.to(dev), k.to(dev), v.to(dev), tensor_layout=layout, is_causal=causal, smooth_k=smooth,
+                      kernel=kernel, return_lse=True)
+    check_status(dev)
+    if kernel == "int8":
+        emu, lse_emu = so.sageattn_emulated(q, k, v, tensor_layout=layout, is_causal=causal, smooth_k=smooth,
+                                            return_lse=True)
+    else:
+        emu, lse_emu = so.direct_attn_emulated(q, k, v, tensor_layout=layout, is_causal=causal, return_lse=True)
+    assert torch.isfinite(o.float()).all()
+    acc = so.accuracy(o.float().cpu(), emu.float())
+    assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, acc
+    assert (lse.cpu() - lse_emu).abs().max().item() < 2e-3
