@@ -78,3 +78,9 @@ def test_invalid_arguments_are_rejected_without_cuda():
     rc = lib.sage_quant_qk_int8(ctypes.byref(k), ctypes.byref(k), None, None, None, 0, 1, 2, 2, 16, 16, 64,
                                 ctypes.c_float(0.125), None, None, None, None, None)
     assert rc == 1
+
+
+def test_graft_entry_build_runs():
+    """The build entry point compiles (or finds up to date) both libraries and checks them."""
+    import __graft_entry__
+    __graft_entry__.build()
