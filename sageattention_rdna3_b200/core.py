@@ -174,7 +174,7 @@ def sageattn(
     if not _aligned(v):
         v = v.contiguous()
 
-    o = torch.empty_like(q)
+    o = None
     lse = None
     want_lse = return_lse and os.environ.get("SAGEATTN_B200_LSE_ZEROS", "0") != "1"
     if return_lse:
@@ -184,42 +184,21 @@ def sageattn(
         else:
             lse = torch.zeros(lse_shape, dtype=torch.float32, device=q.device)
     if q_len == 0 or q_shape[0] == 0 or q_shape[head_dim_idx] == 0:
-        pass
+        o = torch.empty_like(q)
     elif kv_len == 0:
-        o.zero_()                        # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
-    elif _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len):
-        # core.py:141-163: V as fp16 (converted for bf16 inputs), then fp16_attn / bf16_attn.
-        # (The operators set the device guard themselves; nothing here depends on the current device.)
-        if dtype == torch.bfloat16:
-            v16, v_layout = ops.v_to_f16(v, layout), _LAYOUT_CODE["HND"]
-            op = ops.bf16_attn
-        else:
-            v16, v_layout = v, layout
-            op = ops.fp16_attn
-        op(q, k, v16, o, layout, v_layout, int(is_causal), sm_scale, 0, _status_word(q.device),
-           lse if want_lse else None)
-        if os.environ.get("SAGEATTN_B200_CHECK_STATUS", "0") == "1":
-            check_status(q.device)
+        o = torch.zeros_like(q)          # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
     else:
-        if smooth_k:
-            k_mean = ops.mean_seq(k, layout)
-        else:
-            k_mean = torch.empty(0, device=q.device, dtype=q.dtype)
-        if dtype == torch.bfloat16:
-            # P.V runs in fp16 (csrc/attn_gfx11.cu:377-381): one launch quantises Q/K and
-            # writes the fp16 copy of V, [B,Hkv,Skv,D] contiguous.
-            q_int8, q_scale, k_int8, k_scale, v16 = ops.prep_qkv(q, k, v, k_mean, layout, sm_scale)
-            v_layout = _LAYOUT_CODE["HND"]
-        else:
-            q_int8, q_scale, k_int8, k_scale = ops.quant_qk_int8(q, k, k_mean, layout, sm_scale)
-            v16, v_layout = v, layout
-        ops.qk_int8_sv_f16_attn(q_int8, k_int8, v16, o, q_scale, k_scale, layout, v_layout,
-                                int(is_causal), sm_scale, None, _status_word(q.device),
-                                lse if want_lse else None)
-        if want_lse and smooth_k:
+        # core.py:141-198 in one operator call: the un-quantised branch (V as fp16, fp16_attn / bf16_attn)
+        # or the INT8 branch ([K mean,] quantise Q / K and convert a bf16 V in one launch, attention).
+        direct = _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len)
+        smooth = bool(smooth_k) and not direct          # the un-quantised branch has no use for the mean
+        out = ops.sageattn_fwd(q, k, v, layout, int(is_causal), sm_scale, int(smooth), int(direct),
+                               _status_word(q.device), lse if want_lse else None)
+        o = out[0]
+        if want_lse and smooth:
             # the kernel saw k - mean: every score of a row was lowered by sm_scale * q.mean
-            rep = q.size(head_dim_idx) // k.size(head_dim_idx)
-            km = k_mean.float().repeat_interleave(rep, dim=1)                   # [B,Hq,D]
+            rep = q_shape[head_dim_idx] // k_shape[head_dim_idx]
+            km = out[1].float().repeat_interleave(rep, dim=1)                   # [B,Hq,D]
             eq = "bhsd,bhd->bhs" if tensor_layout == "HND" else "bshd,bhd->bhs"
             lse += torch.einsum(eq, q.float(), km) * sm_scale
         if os.environ.get("SAGEATTN_B200_CHECK_STATUS", "0") == "1":

@@ -272,9 +272,40 @@ at::Tensor bf16_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor&
                      "bf16_attn");
 }
 
+// sageattn_fwd(Tensor query, Tensor key, Tensor value, int tensor_layout, int is_causal, float sm_scale,
+//              int smooth_k, int use_direct, Tensor status, Tensor? lse) -> Tensor[]
+// The whole of the reference's sageattn body after its assertions (sageattention/core.py:96-201) in
+// one operator call: allocate the output, then either the un-quantised branch (:141-163: fp16 V,
+// fp16_attn / bf16_attn) or the INT8 branch (:165-198: [mean,] quantise, attention).  Returns
+// [output] or, with smooth_k on the INT8 branch, [output, key_mean] (the caller needs the mean to
+// refer a log-sum-exp to the original keys).  One Python -> C++ crossing instead of two to four.
+std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
+                                     int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
+                                     const at::Tensor& status, const c10::optional<at::Tensor>& lse) {
+  at::Tensor o = at::empty_like(q);
+  const bool bf16 = q.scalar_type() == at::kBFloat16;
+  const c10::optional<at::Tensor> st(status), none;
+  if (use_direct) {
+    if (bf16) {
+      direct_attn(q, k, v_to_f16(v, layout), o, layout, kHND, is_causal, sm_scale, 0, st, lse, at::kBFloat16, "bf16_attn");
+    } else {
+      direct_attn(q, k, v, o, layout, layout, is_causal, sm_scale, 0, st, lse, at::kHalf, "fp16_attn");
+    }
+    return {o};
+  }
+  at::Tensor k_mean = smooth_k ? mean_seq(k, layout) : at::empty({0}, q.options());
+  std::vector<at::Tensor> parts = quant_impl(q, k, k_mean, bf16 ? &v : nullptr, layout, sm_scale);
+  qk_int8_sv_f16_attn(parts[0], parts[2], bf16 ? parts[4] : v, o, parts[1], parts[3], layout, bf16 ? kHND : layout,
+                      is_causal, sm_scale, none, st, lse);
+  if (smooth_k) return {o, k_mean};
+  return {o};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(sageattention, m) {
+  m.def("sageattn_fwd(Tensor query, Tensor key, Tensor value, int tensor_layout, int is_causal, float sm_scale, "
+        "int smooth_k, int use_direct, Tensor status, Tensor? lse=None) -> Tensor[]");
   m.def("fp16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
         "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("bf16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
@@ -290,6 +321,7 @@ TORCH_LIBRARY(sageattention, m) {
 }
 
 TORCH_LIBRARY_IMPL(sageattention, CUDA, m) {
+  m.impl("sageattn_fwd", &sageattn_fwd);
   m.impl("qk_int8_sv_f16_attn", &qk_int8_sv_f16_attn);
   m.impl("fp16_attn", &fp16_attn);
   m.impl("bf16_attn", &bf16_attn);
