@@ -565,7 +565,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     float m_used = kMaskValue;
     float l = 0.0f;
-    bool refused_last = false;
+    int distrust = 0;                     // > 1: the optimistic attempt is skipped (see below)
 
     // k_scale of the next half is fetched one half ahead, off the critical path
     float ks_next[4];
@@ -658,9 +658,10 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       bool done = false;
       float m_half = kMaskValue;
       const bool first_or_masked = (hh == 0) || masked;
-      // The attempt is skipped right after a refused one: data whose maxima keep jumping (heavy
-      // tails) would pay for two exp passes on most steps otherwise.
-      const bool attempt = !first_or_masked && !refused_last;
+      // The attempt is skipped while the data keeps refusing it: a refused attempt or a step that
+      // had to move the maximum raises `distrust`, a step that did not lowers it.  Data whose maxima
+      // keep jumping (heavy tails) would pay for two exp passes on most steps otherwise.
+      const bool attempt = !first_or_masked && distrust < 2;
       if (attempt) {
         const float sum = exp_pass(std::false_type{}, m_used);
         if (!__any_sync(0xffffffffu, !(sum <= kOptimisticSumMax))) {
@@ -668,7 +669,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           done = true;
         }
       }
-      refused_last = attempt && !done;
+      if (attempt) distrust = done ? max(distrust - 1, 0) : min(distrust + 2, 4);
       if (!done && !masked && !QKF) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {                   // scales are >= 0: max commutes with the scaling
@@ -695,7 +696,9 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           // After a refused attempt the bar is lower: a row whose 64 values added up to more
           // than 2^14 has a maximum above 2^8, and it must move or it would be refused again.
           const bool need = m_half > m_used + (attempt ? kRefusedBarLog2 : kLazyRescaleLog2);
-          if (__any_sync(0xffffffffu, need)) {
+          const bool moved = __any_sync(0xffffffffu, need);
+          if (!attempt) distrust = moved ? min(distrust + 1, 4) : distrust - 1;
+          if (moved) {
             // O must be at rest: the P.V of the previous half has to be complete
             const int hp = h ^ 1;
             const int tp = h ? t : t - 1;
