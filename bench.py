@@ -7,17 +7,23 @@ One "step" is one pass of the hot path (K mean when smooth_k, Q/K quantisation +
 fused attention) over one batch of synthetic input of the named workload.  One JSON line is printed:
 
 * ``value``     - attention TOPS, 4*B*Hq*Sq*Skv*D / t (benchmark_attn/benchmark_attn.py:40-47 of the
-                  reference), inputs resident in HBM, aggregated over all ranks.
-* ``e2e``       - the same metric through the public ``sageattn_host()`` call with HOST (pinned) q, k,
-                  v and a host output: the host->device copies and the device->host copy of the
-                  output are inside the timed region (pipelined over streams by that call).
-* ``roofline``  - the fused attention kernel against the tensor-core roofline (executed flops).
+                  reference), timed through ``sageattn()`` on inputs resident in HBM, aggregated over
+                  all ranks (time = max over ranks).
+* ``roofline``  - the fused attention kernel against the tensor-core roofline (executed flops, burst
+                  peak), from a second loop that calls the operators with events around each kernel;
+                  ``roofline_prep`` / ``roofline_kmean`` give the two HBM-bound kernels.
+* ``e2e``       - the same metric through ``sageattn_host()`` with HOST (pinned) q, k, v and a host
+                  output: the copies in both directions are inside the timed region; ``copy_floor_ms``
+                  is the same bytes copied with no compute.
+* ``allgather`` - N > 1: the step with the final NCCL all-gather of the outputs, serial and overlapped.
+* ``configs``   - N = 1: step time / TOPS / roofline fraction of the other benchmark configurations.
 * ``cpu_baseline`` - the CPU oracle (a port of the reference's arithmetic) on the host cores, on a
                   bounded sample of the same workload.
 * ``--impl reference`` - times that CPU oracle only (the reference has no CPU or NVIDIA
                   implementation of its own); rank 0 alone runs it.
-With N > 1 every rank runs the full workload on its own GPU (weak scaling: the global batch is
-N times the workload's); ``--scaling strong`` shards the workload's (batch, kv-head) units instead.
+With N > 1 the workload's (batch, kv-head) units are sharded over the ranks (strong scaling: every
+rank generates and holds only its own units, no collective on the data path); ``--scaling weak``
+runs the whole workload on every rank instead.
 """
 from __future__ import annotations
 
@@ -45,6 +51,7 @@ WORKLOADS = {
 }
 DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
 METRIC = "attention TOPS (4*B*H*S^2*D/t)"
+DTYPE_NOTE = "int8 x int8 -> int32 (QK^T), fp16 x fp16 -> fp32 (PV), fp32 softmax"
 # dram__bytes_read.sum + dram__bytes_write.sum of one sage_attn_kernel launch, from an ncu capture of
 # this workload (ncu --set full -k regex:sage_ on `bench.py --steps 1 --warmup 3`)
 ATTN_TRAFFIC_BYTES = {"C3": 379.3e6}
@@ -174,16 +181,18 @@ def cpu_oracle_run(w, name, steps, warmup):
 
 
 def run_reference(args, w, name, rank):
+    """The reference arm: the CPU oracle (a port of the reference's arithmetic; the reference has no
+    CPU or NVIDIA implementation of its own) on the host cores, ``--warmup`` + ``--steps`` runs of a
+    bounded sample (one (batch, kv-head) unit) of the workload."""
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    warmup = 1 if args.warmup > 0 else 0
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
     tops, sample, threads = cpu_oracle_run(w, name, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": cpu_oracle_run.last_ms, "higher_is_better": True,
-        "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8 x int8 -> int32 (QK^T), fp16 x fp16 -> fp32 (PV)", "data": "synthetic",
+        "scaling": "strong",
+        "vs_baseline": None, "dtype": DTYPE_NOTE, "data": "synthetic",
         "config": {"workload": workload_string(name, w)},
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -199,6 +208,282 @@ def workload_string(name, w):
             f"{'causal' if w['causal'] else 'non-causal'} smooth_k={w['smooth_k']}")
 
 
+def bind_near_gpu(index):
+    """Run this process on the CPU cores NVML lists as local to GPU ``index`` (when it says so), so
+    that pinned host buffers allocated afterwards are first touched on that socket.  Only this
+    process's own CPU affinity changes; nothing on the GPU or the host is reconfigured."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        n_words = (os.cpu_count() + 63) // 64
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, n_words)
+        cpus = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (int(wd) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
+class Problem:
+    """One rank's share of a workload: ``units`` (batch, kv-head) units laid out as a batch of
+    single-kv-head problems (identical work and memory traffic to a [B, H] slab), resident in HBM."""
+
+    def __init__(self, w, name, units, full, seed_offset, dev, ops, lib):
+        self.w, self.name, self.dev, self.ops = w, name, dev, ops
+        rep = w["Hq"] // w["Hkv"]
+        if full:
+            self.host = make_inputs(w, name, seed_offset=seed_offset)
+            self.Bl, self.Hql, self.Hkvl = w["B"], w["Hq"], w["Hkv"]
+        else:
+            self.host = make_inputs(w, name, seed_offset=seed_offset, heads=(rep, 1), batch=units)
+            self.Bl, self.Hql, self.Hkvl = units, rep, 1
+        self.units = units
+        self.nominal = 4.0 * self.Bl * self.Hql * w["S"] * w["S"] * w["D"]
+        self.executed = self.nominal * (executed_ops(w) / nominal_ops(w))
+        self.layout_code = 1 if w["layout"] == "HND" else 0
+        self.sm_scale = w["D"] ** -0.5
+        self.q, self.k, self.v = (t.to(dev) for t in self.host)
+        self.o = torch.empty_like(self.q)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.empty_mean = torch.empty(0, device=dev, dtype=self.q.dtype)
+        self.attn_events, self.prep_events, self.mean_events = [], [], []
+        self.launches_per_step = 2 + (1 if w["smooth_k"] else 0)
+        # a problem that fills the GPU unevenly runs on persistent CTAs and adds the merge kernel
+        if lib.sage_attn_workspace_bytes(self.Bl, self.Hql, w["S"], w["S"], w["D"], int(w["causal"])) > 0:
+            self.launches_per_step += 1
+
+    @staticmethod
+    def _ev():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def step_ops(self, record=False, o=None):
+        """The hot path as its operators, optionally with CUDA events around each kernel."""
+        w, ops = self.w, self.ops
+        o = self.o if o is None else o
+        m0 = self._ev() if record else None
+        k_mean = ops.mean_seq(self.k, self.layout_code) if w["smooth_k"] else self.empty_mean
+        p0 = self._ev() if record else None
+        if self.q.dtype == torch.bfloat16:
+            q8, qs, k8, ks, v16 = ops.prep_qkv(self.q, self.k, self.v, k_mean, self.layout_code, self.sm_scale)
+            vl = 1
+        else:
+            q8, qs, k8, ks = ops.quant_qk_int8(self.q, self.k, k_mean, self.layout_code, self.sm_scale)
+            v16, vl = self.v, self.layout_code
+        if record:
+            e0 = self._ev()
+            self.mean_events.append((m0, p0))
+            self.prep_events.append((p0, e0))
+        ops.qk_int8_sv_f16_attn(q8, k8, v16, o, qs, ks, self.layout_code, int(w["causal"]), self.sm_scale,
+                                value_layout=vl, status=self.status)
+        if record:
+            self.attn_events.append((e0, self._ev()))
+        return o
+
+    def step_public(self):
+        """The same step through the public call."""
+        from sageattention_rdna3_b200 import sageattn
+        w = self.w
+        return sageattn(self.q, self.k, self.v, tensor_layout=w["layout"], is_causal=w["causal"],
+                        smooth_k=w["smooth_k"], kernel="int8")
+
+    def kernel_ms(self):
+        avg = lambda evs: sum(a.elapsed_time(b) for a, b in evs) / max(len(evs), 1)
+        return avg(self.attn_events), avg(self.prep_events), avg(self.mean_events)
+
+    def hbm_bytes(self):
+        """Algorithmic bytes of the two HBM-bound kernels on this rank."""
+        w, e = self.w, self.q.element_size()
+        nq, nk = self.q.numel(), self.k.numel()
+        n_scales = self.Bl * self.Hql * ((w["S"] + 31) // 32) + self.Bl * self.Hkvl * ((w["S"] + 15) // 16)
+        prep = nq * e + nk * e + nq + nk + 4 * n_scales + (nk * (e + 2) if self.q.dtype == torch.bfloat16 else 0)
+        mean = nk * e + self.Bl * self.Hkvl * w["D"] * e
+        return prep, mean
+
+
+def timed(fn, steps, barrier):
+    """ms per call of ``fn`` over ``steps`` calls: CUDA events on the launching stream, a barrier and
+    a device synchronize on both sides."""
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        fn(i)
+    t1.record()
+    barrier()
+    return t0.elapsed_time(t1) / steps
+
+
+def measure_gather(prob, steps, warmup, barrier, world, dist, sizes):
+    """The optional final all-gather of the outputs (NCCL over NVLink), two ways: serial (each step
+    computes, then gathers, on one stream) and overlapped (the gather of step i runs on a side
+    stream while step i+1 computes into the other of two output buffers).  Returns ms per step of
+    both, the gather alone, and the bytes every rank receives."""
+    dev, w = prob.dev, prob.w
+    n_max = max(sizes)
+    padded = len(set(sizes)) > 1
+    unit_shape = tuple(prob.o.shape[1:])
+    outs = [torch.empty((n_max,) + unit_shape, dtype=prob.o.dtype, device=dev) for _ in range(2)]
+    fulls = [torch.empty((world * n_max,) + unit_shape, dtype=prob.o.dtype, device=dev) for _ in range(2)]
+    views = [o[:prob.units] if prob.units > 0 else o[:0] for o in outs]
+
+    def finish(full):
+        # NHD: a rank's units are [n, S, heads, D] slabs; the caller's [B, S, H, D] needs one local permute
+        if w["layout"] == "NHD":
+            return full.permute(1, 0, 2, 3).contiguous()
+        return full
+
+    def serial(i):
+        if prob.units > 0:
+            prob.step_ops(o=views[0])
+        dist.all_gather_into_tensor(fulls[0], outs[0])
+        finish(fulls[0])
+
+    side = torch.cuda.Stream(device=dev)
+    gathered = [None, None]
+
+    def overlapped(i):
+        b = i & 1
+        cur = torch.cuda.current_stream(dev)
+        if gathered[b] is not None:
+            cur.wait_event(gathered[b])           # the gather of step i-2 has read this buffer
+        if prob.units > 0:
+            prob.step_ops(o=views[b])
+        computed = torch.cuda.Event()
+        computed.record(cur)
+        with torch.cuda.stream(side):
+            side.wait_event(computed)
+            dist.all_gather_into_tensor(fulls[b], outs[b])
+            finish(fulls[b])
+            e = torch.cuda.Event()
+            e.record(side)
+            gathered[b] = e
+
+    def drain(_=None):
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    def alone(i):
+        dist.all_gather_into_tensor(fulls[0], outs[0])
+        finish(fulls[0])
+
+    res = {}
+    for key, fn in (("serial_ms", serial), ("gather_alone_ms", alone)):
+        for i in range(warmup):
+            fn(i)
+        res[key] = timed(fn, steps, barrier)
+    for i in range(warmup):
+        overlapped(i)
+    drain()
+
+    def overlapped_all(i):
+        overlapped(i)
+        if i == steps - 1:
+            drain()
+
+    res["overlapped_ms"] = timed(overlapped_all, steps, barrier)
+    elem = prob.o.element_size()
+    per_unit = elem
+    for d in unit_shape:
+        per_unit *= d
+    res["recv_bytes_per_rank"] = per_unit * (sum(sizes) - prob.units)
+    res["padded"] = padded
+    return res
+
+
+def measure_e2e(prob, steps, barrier):
+    """End to end through ``sageattn_host()``: pinned host q, k, v in, pinned host output back, every
+    step.  Also times the bare copies of the same bytes (host->device on one stream, device->host on
+    another, no compute): the floor this box's host link puts under the call."""
+    from sageattention_rdna3_b200 import sageattn_host
+    w, dev = prob.w, prob.dev
+    qp, kp, vp = (t.pin_memory() for t in prob.host)
+    o_host = torch.empty(qp.shape, dtype=qp.dtype).pin_memory()
+    layout = w["layout"]
+
+    def step(_):
+        sageattn_host(qp, kp, vp, out=o_host, tensor_layout=layout, is_causal=w["causal"], smooth_k=w["smooth_k"],
+                      device=dev, kernel="int8")
+
+    for i in range(3):
+        step(i)
+    ms = timed(step, steps, barrier)
+
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    qd, kd, vd = (torch.empty_like(t, device=dev) for t in (qp, kp, vp))
+
+    def copies(_):
+        cur = torch.cuda.current_stream(dev)
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            qd.copy_(qp, non_blocking=True)
+            kd.copy_(kp, non_blocking=True)
+            vd.copy_(vp, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            o_host.copy_(prob.o, non_blocking=True)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+
+    for i in range(2):
+        copies(i)
+    floor = timed(copies, steps, barrier)
+    h2d = sum(t.numel() * t.element_size() for t in (qp, kp, vp))
+    d2h = o_host.numel() * o_host.element_size()
+    return {"ms": ms, "copy_floor_ms": floor, "h2d": h2d, "d2h": d2h}
+
+
+def roofline_records(prob, attn_ms, prep_ms, mean_ms, peaks, capped):
+    """Roofline objects of the three kernels from their event-timed launches on this rank."""
+    w = prob.w
+    # Half of the executed operations are int8 (QK^T, taken as 2x the bf16 rate), half fp16 (PV):
+    # time = F/2/(2P) + F/2/P, a blended peak of P/0.75 with P the measured cuBLAS bf16 rate.  The
+    # fraction is quoted on the burst figure (an event-timed kernel); the sustained one is beside it.
+    peak_burst = peaks["bf16_tflops"] / 0.75
+    peak_sustained = peaks["bf16_tflops_sustained"] / 0.75
+    achieved = (prob.executed / (attn_ms / 1e3)) / 1e12
+    total_units = w["B"] * w["Hkv"]
+    traffic = ATTN_TRAFFIC_BYTES.get(prob.name)
+    if traffic is not None:
+        traffic = traffic * prob.units / total_units      # DRAM bytes grow in proportion to the units
+    out = {"roofline": {
+        "bound": "tensor", "kernel": "sage_attn_kernel", "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s",
+        "frac": achieved / peak_burst, "traffic": traffic, "ms_per_launch": attn_ms,
+        "frac_of_sustained_peak": achieved / peak_sustained, "power_capped_during_run": capped,
+        "peak_source": f"{peaks['source']}: cuBLAS bf16 {peaks['bf16_tflops']} TFLOP/s (burst), int8 taken as 2x; "
+                       "executed flops, half int8 half fp16"}}
+    prep_bytes, mean_bytes = prob.hbm_bytes()
+    out["roofline_prep"] = {"bound": "hbm", "kernel": "sage_prep_kernel", "achieved": prep_bytes / (prep_ms / 1e3) / 1e9,
+                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": prep_bytes / (prep_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "ms_per_launch": prep_ms,
+                            "bytes": prep_bytes}
+    if w["smooth_k"] and mean_ms > 0:
+        out["roofline_kmean"] = {"bound": "hbm", "kernel": "sage_kmean_kernel",
+                                 "achieved": mean_bytes / (mean_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": mean_bytes / (mean_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "ms_per_launch": mean_ms,
+                                 "bytes": mean_bytes}
+    return out
+
+
+def run_extra_config(name, dev, ops, lib, peaks, steps=10, warmup=3):
+    """One of the other benchmark configurations on one GPU: step time, TOPS and the attention
+    kernel's roofline fraction, from the operator loop with events."""
+    w = dict(WORKLOADS[name])
+    prob = Problem(w, name, w["B"] * w["Hkv"], True, 0, dev, ops, lib)
+    for _ in range(warmup):
+        prob.step_ops()
+    ms = timed(lambda i: prob.step_ops(record=True), steps, torch.cuda.synchronize)
+    attn_ms, prep_ms, _ = prob.kernel_ms()
+    achieved = prob.executed / (attn_ms / 1e3) / 1e12
+    return {"workload": workload_string(name, w), "ms_per_step": ms, "tops": prob.nominal / (ms / 1e3) / 1e12,
+            "attn_ms": attn_ms, "prep_ms": prep_ms, "attn_executed_tflops": achieved,
+            "attn_frac_of_burst_peak": achieved / (peaks["bf16_tflops"] / 0.75), "steps": steps}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,11 +491,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="C3", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: 'strong' shards the workload's (batch, kv-head) units over the ranks (default); "
+                         "'weak' runs the whole workload on every rank (independent replicas)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-gather", action="store_true")
+    ap.add_argument("--no-extra-configs", action="store_true")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -221,73 +509,21 @@ def main():
     if args.impl == "reference":
         run_reference(args, w, name, rank)
         return
+    args.warmup = max(args.warmup, 3)
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (NVIDIA B200); there is no CPU path")
+    cores_near_gpu = bind_near_gpu(local_rank)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     import torch.distributed as dist
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    from sageattention_rdna3_b200 import _native, check_status, sageattn_host
+    from sageattention_rdna3_b200 import _native, check_status
     from sageattention_rdna3_b200.shard import plan_shards
     ops = _native.load_ops()
-
-    # ---- this rank's share of the work
-    if args.scaling == "strong" and world > 1:
-        shard = plan_shards(w["B"], w["Hq"], w["Hkv"], world)[rank]
-        local_units = shard.n_units
-    else:
-        local_units = w["B"] * w["Hkv"]
-    rep = w["Hq"] // w["Hkv"]
-    # A rank's units are laid out as a batch of single-kv-head problems: identical work and
-    # memory traffic to a [B, H] slab, and it lets any number of units be expressed.
-    if local_units == w["B"] * w["Hkv"]:
-        q_h, k_h, v_h = make_inputs(w, name, seed_offset=100 * rank if args.scaling == "weak" else 0)
-        Bl, Hql, Hkvl = w["B"], w["Hq"], w["Hkv"]
-    else:
-        q_h, k_h, v_h = make_inputs(w, name, seed_offset=100 * rank, heads=(rep, 1), batch=local_units)
-        Bl, Hql, Hkvl = local_units, rep, 1
-    local_nominal = 4.0 * Bl * Hql * w["S"] * w["S"] * w["D"]
-    local_executed = local_nominal * (executed_ops(w) / nominal_ops(w))
-    layout_code = 1 if w["layout"] == "HND" else 0
-    sm_scale = w["D"] ** -0.5
-    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
-    o = torch.empty_like(q)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    empty_mean = torch.empty(0, device=dev, dtype=q.dtype)
-
-    attn_events, prep_events, mean_events = [], [], []
-
-    def ev():
-        e = torch.cuda.Event(enable_timing=True)
-        e.record()
-        return e
-
-    def step(record):
-        m0 = ev() if record else None
-        k_mean = ops.mean_seq(k, layout_code) if w["smooth_k"] else empty_mean
-        p0 = ev() if record else None
-        if q.dtype == torch.bfloat16:
-            q8, qs, k8, ks, v16 = ops.prep_qkv(q, k, v, k_mean, layout_code, sm_scale)
-            vl = 1
-        else:
-            q8, qs, k8, ks = ops.quant_qk_int8(q, k, k_mean, layout_code, sm_scale)
-            v16, vl = v, layout_code
-        if record:
-            e0 = ev()
-            mean_events.append((m0, p0))
-            prep_events.append((p0, e0))
-        ops.qk_int8_sv_f16_attn(q8, k8, v16, o, qs, ks, layout_code, vl, int(w["causal"]), sm_scale, None, status)
-        if record:
-            attn_events.append((e0, ev()))
-
-    launches_per_step = 2 + (1 if w["smooth_k"] else 0)
-    # a problem that fills the GPU unevenly runs on persistent CTAs and adds the merge kernel
     lib = _native.load_abi()
-    if lib.sage_attn_workspace_bytes(Bl, Hql, w["S"], w["S"], w["D"], int(w["causal"])) > 0:
-        launches_per_step += 1
 
     def barrier():
         torch.cuda.synchronize()
@@ -295,109 +531,97 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # ---- this rank's share of the work: its own units only, generated here
+    total_units = w["B"] * w["Hkv"]
+    strong = args.scaling == "strong"
+    sizes = [s.n_units for s in plan_shards(w["B"], w["Hq"], w["Hkv"], world)] if strong else [total_units] * world
+    units = sizes[rank]
+    prob = Problem(w, name, units, full=(units == total_units), seed_offset=100 * rank, dev=dev, ops=ops, lib=lib)
+
     sampler = ClockSampler(local_rank)
+    gather = e2e = None
     with sampler:
+        # (1) the step through the public call: this is `value`
         for _ in range(args.warmup):
-            step(False)
-        barrier()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(args.steps):
-            step(True)
-        t1.record()
-        barrier()
-        ms_total = t0.elapsed_time(t1)
-        attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
-        prep_ms = sum(a.elapsed_time(b) for a, b in prep_events) / len(prep_events)
-        mean_ms = sum(a.elapsed_time(b) for a, b in mean_events) / len(mean_events)
-
-        # ---- end to end through sageattn(): host (pinned) inputs in, host output back, every step
-        e2e = None
+            prob.step_public()
+        ms_public = timed(lambda i: prob.step_public(), args.steps, barrier)
+        # (2) the same step as its operators with events around every kernel: the rooflines
+        for _ in range(args.warmup):
+            prob.step_ops()
+        ms_ops = timed(lambda i: prob.step_ops(record=True), args.steps, barrier)
+        attn_ms, prep_ms, mean_ms = prob.kernel_ms()
+        # (3) with the final all-gather of the outputs
+        if world > 1 and strong and not args.no_gather:
+            gather = measure_gather(prob, args.steps, args.warmup, barrier, world, dist, sizes)
+        # (4) end to end with host buffers
         if not args.no_e2e:
-            qp, kp, vp = q_h.pin_memory(), k_h.pin_memory(), v_h.pin_memory()
-            o_host = torch.empty(q_h.shape, dtype=q_h.dtype).pin_memory()
-            e2e_steps = max(3, min(args.steps, 20))
-
-            def e2e_step():
-                sageattn_host(qp, kp, vp, out=o_host, tensor_layout=w["layout"], is_causal=w["causal"],
-                              smooth_k=w["smooth_k"], device=dev)
-
-            for _ in range(3):
-                e2e_step()
-            barrier()
-            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s0.record()
-            for _ in range(e2e_steps):
-                e2e_step()
-            s1.record()
-            barrier()
-            e2e_ms = s0.elapsed_time(s1) / e2e_steps
-            e2e = (e2e_ms, q_h.numel() * q_h.element_size() + 2 * k_h.numel() * k_h.element_size(),
-                   o_host.numel() * o_host.element_size())
+            e2e = measure_e2e(prob, max(3, min(args.steps, 20)), barrier)
     check_status(dev)
 
-    ms_step = ms_total / args.steps
-    stats = torch.tensor([ms_step, attn_ms, e2e[0] if e2e else 0.0], dtype=torch.float64, device=dev)
-    units = torch.tensor([local_nominal, local_executed], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(units, op=dist.ReduceOp.SUM)
-    ms_step, attn_ms_max, e2e_ms = (float(x) for x in stats.tolist())
-    total_nominal, total_executed = (float(x) for x in units.tolist())
+    def over_ranks(values, op):
+        t = torch.tensor(values, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=op)
+        return [float(x) for x in t.tolist()]
+
+    MAX, SUM = dist.ReduceOp.MAX, dist.ReduceOp.SUM
+    g = gather or {}
+    ms_public, ms_ops, attn_ms_max, ser_ms, ovl_ms, alone_ms, e2e_ms, floor_ms = over_ranks(
+        [ms_public, ms_ops, attn_ms, g.get("serial_ms", 0.0), g.get("overlapped_ms", 0.0), g.get("gather_alone_ms", 0.0),
+         e2e["ms"] if e2e else 0.0, e2e["copy_floor_ms"] if e2e else 0.0], MAX)
+    total_nominal, total_executed, h2d_total, d2h_total = over_ranks(
+        [prob.nominal, prob.executed, e2e["h2d"] if e2e else 0.0, e2e["d2h"] if e2e else 0.0], SUM)
 
     if rank == 0:
         peaks = measured_peaks()
         clocks = sampler.summary()
-        # Half of the executed operations are int8 (QK^T, taken as 2x the bf16 rate), half fp16
-        # (PV): time = F/2/(2P) + F/2/P, i.e. a blended peak of P/0.75.  P is the measured cuBLAS
-        # bf16 rate: the sustained (power-capped) figure when this run itself was power capped
-        # (the kernel is timed inside a long back-to-back loop), the burst figure otherwise.
         capped = "sw_power_cap" in clocks["reasons"]
-        peak_burst = peaks["bf16_tflops"] / 0.75
-        peak_sustained = peaks["bf16_tflops_sustained"] / 0.75
-        blended_peak = peak_sustained if capped else peak_burst
-        achieved = (local_executed / (attn_ms / 1e3)) / 1e12
-        # algorithmic bytes of the HBM-bound kernels on this rank
-        e = q.element_size()
-        nq, nk = q.numel(), k.numel()
-        n_scales = Bl * Hql * ((w["S"] + 31) // 32) + Bl * Hkvl * ((w["S"] + 15) // 16)
-        prep_bytes = nq * e + nk * e + nq + nk + 4 * n_scales + (nk * (e + 2) if q.dtype == torch.bfloat16 else 0)
-        mean_bytes = nk * e + Bl * Hkvl * w["D"] * e
+        tops = lambda ms: total_nominal / (ms / 1e3) / 1e12
+        in_bytes = 3 * prob.q.numel() * prob.q.element_size() if prob.units else 0
         line = {
-            "metric": METRIC, "value": total_nominal / (ms_step / 1e3) / 1e12, "unit": "TOPS",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-            "dtype": "int8 x int8 -> int32 (QK^T), fp16 x fp16 -> fp32 (PV), fp32 softmax", "data": "synthetic",
-            "config": {"workload": workload_string(name, w), "per_gpu": f"B={Bl} Hq={Hql} Hkv={Hkvl}",
-                       "l2": "inputs larger than L2, no flush" if q.numel() * 2 * 3 > 126e6 else "inputs fit in L2, no flush",
-                       "executed_tops": total_executed / (ms_step / 1e3) / 1e12},
-            "roofline": {"bound": "tensor", "kernel": "sage_attn_kernel", "achieved": achieved, "peak": blended_peak,
-                         "unit": "TFLOP/s", "frac": achieved / blended_peak, "traffic": ATTN_TRAFFIC_BYTES.get(name),
-                         "ms_per_launch": attn_ms,
-                         "frac_of_burst_peak": achieved / peak_burst, "frac_of_sustained_peak": achieved / peak_sustained,
-                         "peak_source": f"{peaks['source']}: cuBLAS bf16 {peaks['bf16_tflops_sustained'] if capped else peaks['bf16_tflops']} "
-                                        f"TFLOP/s ({'sustained, this run was power capped' if capped else 'burst'}), "
-                                        "int8 taken as 2x; executed flops, half int8 half fp16"},
-            "roofline_prep": {"bound": "hbm", "kernel": "sage_prep_kernel", "achieved": prep_bytes / (prep_ms / 1e3) / 1e9,
-                              "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                              "frac": prep_bytes / (prep_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "ms_per_launch": prep_ms,
-                              "bytes": prep_bytes},
-            "gpu_launches": launches_per_step * args.steps,
+            "metric": METRIC, "value": tops(ms_public), "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_public, "higher_is_better": True,
+            "scaling": args.scaling if world > 1 else "strong", "vs_baseline": None, "dtype": DTYPE_NOTE,
+            "data": "synthetic",
+            "config": {"workload": workload_string(name, w)},
+            "per_gpu": {"units": sizes, "shape": f"B={prob.Bl} Hq={prob.Hql} Hkv={prob.Hkvl}",
+                        "l2": "inputs larger than L2, no flush" if in_bytes > 126e6 else "inputs fit in L2, no flush"},
+            "timed_call": "sageattn(q, k, v, kernel='int8') on HBM-resident inputs, max over ranks",
+            "executed_tops": total_executed / (ms_public / 1e3) / 1e12,
+            "operator_loop": {"ms_per_step": ms_ops, "value": tops(ms_ops),
+                              "note": "the same step as mean_seq / prep_qkv / qk_int8_sv_f16_attn with events around "
+                                      "each kernel; the rooflines come from it"},
+            "gpu_launches": prob.launches_per_step * args.steps,
             "clocks": clocks,
         }
-        if w["smooth_k"]:
-            line["roofline_kmean"] = {"bound": "hbm", "kernel": "sage_kmean_kernel",
-                                      "achieved": mean_bytes / (mean_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"],
-                                      "unit": "GB/s", "frac": mean_bytes / (mean_ms / 1e3) / 1e9 / peaks["hbm_gbs"],
-                                      "ms_per_launch": mean_ms, "bytes": mean_bytes}
+        line.update(roofline_records(prob, attn_ms, prep_ms, mean_ms, peaks, capped))
+        if gather:
+            recv = gather["recv_bytes_per_rank"]
+            line["allgather"] = {
+                "collective": "NCCL all_gather_into_tensor of O" + (" + local permute (NHD)" if w["layout"] == "NHD" else ""),
+                "recv_bytes_per_rank": recv, "nvlink_floor_ms": recv / 770e9 * 1e3,
+                "gather_alone_ms": alone_ms,
+                "serial": {"ms_per_step": ser_ms, "value": tops(ser_ms)},
+                "overlapped": {"ms_per_step": ovl_ms, "value": tops(ovl_ms),
+                               "how": "gather of step i on a side stream while step i+1 computes (two output buffers)"},
+            }
         if e2e:
-            line["e2e"] = {"value": total_nominal / (e2e_ms / 1e3) / 1e12, "unit": "TOPS",
-                           "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2], "ms_per_step": e2e_ms}
-        if not args.no_cpu_baseline and world == 1:
-            tops, sample, threads = cpu_oracle_run(w, name, 2, 1)
-            line["cpu_baseline"] = {"value": tops, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample}
+            line["e2e"] = {"value": tops(e2e_ms), "unit": "TOPS", "h2d_bytes_per_step": int(h2d_total),
+                           "d2h_bytes_per_step": int(d2h_total), "ms_per_step": e2e_ms, "copy_floor_ms": floor_ms,
+                           "of_copy_floor": floor_ms / e2e_ms if e2e_ms > 0 else None,
+                           "host_cores_bound_near_gpu": cores_near_gpu,
+                           "call": "sageattn_host(): pinned host q, k, v in, pinned host output back, every step; "
+                                   "copy_floor_ms = the same bytes copied with no compute, all ranks at once"}
+        if world == 1 and not args.no_extra_configs:
+            del prob
+            torch.cuda.empty_cache()
+            line["configs"] = {n: run_extra_config(n, dev, ops, lib, peaks) for n in ("C2", "C4", "C5") if n != name}
+        if world == 1 and not args.no_cpu_baseline:
+            c_tops, sample, threads = cpu_oracle_run(w, name, 2, 1)
+            line["cpu_baseline"] = {"value": c_tops, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

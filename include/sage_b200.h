@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SAGE_ABI_VERSION 3
+#define SAGE_ABI_VERSION 4
 
 #define SAGE_DTYPE_F16 0
 #define SAGE_DTYPE_BF16 1
@@ -42,6 +42,22 @@ typedef struct sage_strided {
 
 int sage_abi_version(void);
 const char* sage_last_error(void);
+
+/* The `status` word of the attention entry points (optional, a device int32 the caller zeroes):
+ * the kernels write a non-zero code there when they had to give up (1 = shared memory misaligned,
+ * 2 + 16*k = the bounded wait on barrier k ran out) and return instead of hanging; CTAs that start
+ * while the word is already non-zero return at once, so a failed launch costs about one wait bound
+ * and later launches do nothing until the caller has read and cleared the word.  With status ==
+ * NULL such a failure goes unreported and the output is left partly unwritten.  The reference has
+ * no counterpart (its launchers check nothing after the launch, csrc/attn_gfx11.cu:2069-2273).
+ *
+ * Test hooks, for the failure-detection tests only (process-wide, not for production use; no
+ * counterpart in the reference).  sage_test_set_wait_limit_us shortens the bound of every barrier
+ * wait in the attention kernels (us <= 0 restores the default of about one second);
+ * sage_test_drop_v_load(1) makes the TMA producer skip the V load of the first KV tile, so that a
+ * wait runs out for real - it is honoured only while a shortened bound is set. */
+int sage_test_set_wait_limit_us(long long us);
+int sage_test_drop_v_load(int on);
 
 /* Mean of K over the sequence, per (batch, head, channel), in the input dtype.
  * Replaces mean_seq_gfx11 (csrc/attn_gfx11.h:48; csrc/attn_gfx11.cu:1937-1972, kernel :94-145):

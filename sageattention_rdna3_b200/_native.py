@@ -55,6 +55,10 @@ def load_abi() -> ctypes.CDLL:
     lib.sage_abi_version.argtypes = []
     lib.sage_last_error.restype = ctypes.c_char_p
     lib.sage_last_error.argtypes = []
+    lib.sage_test_set_wait_limit_us.restype = i
+    lib.sage_test_set_wait_limit_us.argtypes = [ctypes.c_longlong]
+    lib.sage_test_drop_v_load.restype = i
+    lib.sage_test_drop_v_load.argtypes = [i]
     lib.sage_mean_seq.restype = i
     lib.sage_mean_seq.argtypes = [sp, i, i, i, i, i, vp, vp]
     lib.sage_quant_qk_int8.restype = i

@@ -21,6 +21,9 @@ _BACKEND = "native"          # the reference's scripts read this name (core.py:8
 _LAYOUT_CODE = {"NHD": 0, "HND": 1}   # csrc/attn_gfx11.cu:32-33
 
 _status_words: Dict[int, torch.Tensor] = {}
+_status_mirrors: Dict[int, tuple] = {}
+_STATUS_MESSAGE = ("sageattn: the attention kernel reported device status {code} "
+                   "(1 = shared memory misaligned, 2+16*k = bounded wait k timed out)")
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -31,6 +34,23 @@ def _status_word(device: torch.device) -> torch.Tensor:
         word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _status_words[idx] = word
     return word
+
+
+def _status_mirror(device: torch.device):
+    """A pinned host copy of the device's status word (tensor, numpy view).  Every ``sageattn`` call
+    enqueues a 4-byte copy into it behind its kernels and looks at it before it launches: a kernel
+    that gave up is reported by the next call on that device at the latest, without any
+    synchronisation.  ``SAGEATTN_B200_STATUS_MIRROR=0`` switches the copy off."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    pair = _status_mirrors.get(idx)
+    if pair is None:
+        host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        pair = (host, host.numpy())
+        _status_mirrors[idx] = pair
+    return pair
+
+
+_MIRROR_ON = os.environ.get("SAGEATTN_B200_STATUS_MIRROR", "1") != "0"
 
 
 def check_status(device: Union[torch.device, int, str, None] = None) -> None:
@@ -45,8 +65,9 @@ def check_status(device: Union[torch.device, int, str, None] = None) -> None:
     code = int(word.item())
     if code != 0:
         word.zero_()
-        raise RuntimeError(f"sageattn: the attention kernel reported device status {code} "
-                           "(1 = shared memory misaligned, 2+16*k = bounded wait k timed out)")
+        if _MIRROR_ON:
+            _status_mirror(device)[1][0] = 0
+        raise RuntimeError(_STATUS_MESSAGE.format(code=code))
 
 
 def _aligned(t: torch.Tensor) -> bool:
@@ -125,6 +146,13 @@ def sageattn(
     quantised scores (with ``smooth_k`` the kernel works on centred keys and ``sm_scale * q.mean(k)``
     is added back, so the value refers to the caller's keys).  The reference returns zeros there as
     a placeholder (``core.py:203-211``); ``SAGEATTN_B200_LSE_ZEROS=1`` restores that.
+
+    Errors on the device.  Every wait inside the kernels is bounded; a kernel that has to give up
+    writes a code to a per-device status word and returns, leaving the output partly unwritten.  The
+    call itself never synchronises, so it cannot raise for its own launch: the failure is raised by
+    the NEXT ``sageattn`` call on that device (the word is mirrored to pinned host memory behind
+    every call), by ``check_status()`` (synchronises), or at once with
+    ``SAGEATTN_B200_CHECK_STATUS=1`` (synchronises every call).  The reference has no such state.
     """
     dtype = q.dtype
     assert q.is_cuda, "Input tensors must be on CUDA/HIP device."
@@ -192,8 +220,16 @@ def sageattn(
         # or the INT8 branch ([K mean,] quantise Q / K and convert a bf16 V in one launch, attention).
         direct = _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len)
         smooth = bool(smooth_k) and not direct          # the un-quantised branch has no use for the mean
+        mirror = None
+        if _MIRROR_ON:
+            mirror, seen = _status_mirror(q.device)
+            if seen[0] != 0:                            # an earlier call on this device gave up
+                code = int(seen[0])
+                seen[0] = 0
+                _status_word(q.device).zero_()
+                raise RuntimeError(_STATUS_MESSAGE.format(code=code) + "; reported by the call after the one that failed")
         out = ops.sageattn_fwd(q, k, v, layout, int(is_causal), sm_scale, int(smooth), int(direct),
-                               _status_word(q.device), lse if want_lse else None)
+                               _status_word(q.device), lse if want_lse else None, mirror)
         o = out[0]
         if want_lse and smooth:
             # the kernel saw k - mean: every score of a row was lowered by sm_scale * q.mean

@@ -280,7 +280,10 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   int* fail_code = reinterpret_cast<int*>(smem + L::kOffMisc + 8);
 
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    // A status word that is already set means an earlier CTA of this launch (or an earlier launch
+    // the caller has not looked at yet) gave up: this CTA leaves through the abort path at once, so a
+    // failing launch costs about one wait bound and not one per wave of CTAs.
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     *fail_code = 0;
   }
   // TMA loads of the producer thread.  int8 Q / K are contiguous [B*H, S, D] (3-D maps); 16-bit Q / K
@@ -346,6 +349,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool dead_on_arrival = *abort_flag != 0;
 
 // A failed wait records which barrier it was and leaves the role's loop.
 #ifndef SAGE_HINT_TMA
@@ -364,7 +368,9 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 #define SAGE_WAIT_OR(bar_ptr, parity, bar_id, action) SAGE_WAIT_ROLE_OR(kHintRole, bar_ptr, parity, bar_id, action)
 
-  if (warp == 4) {
+  if (dead_on_arrival) {
+    // nothing to do: the first loads of the producer land during the teardown wait
+  } else if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     constexpr bool kHintRole = SAGE_HINT_TMA;
     // Per segment: Q, K(first tile), then for every tile K(j+1) before V(j): K is needed first.  Q and

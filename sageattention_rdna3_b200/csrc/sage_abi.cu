@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -22,6 +23,8 @@ static __device__ __align__(256) unsigned char g_static_kmean[SAGE_STATIC_KMEAN_
 namespace {
 
 thread_local char g_err[512] = "";
+std::atomic<long long> g_wait_limit_cycles{sage::kWaitLimitCycles};
+std::atomic<int> g_test_drop_v_load{0};
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -148,29 +151,41 @@ void fill_attn_params(sage::AttnParams* pp, void* o, int64_t o_stride_b, int64_t
   p.lse = lse;
   p.status = status;
   // Every barrier wait in the kernel gives up after this many SM clocks (about one second) and
-  // reports through `status`.  Two environment variables exist for the failure-detection test only:
-  // SAGE_WAIT_LIMIT_US shortens the bound, SAGE_TEST_DROP_V_LOAD makes a wait run out on purpose.
-  p.wait_limit_cycles = sage::kWaitLimitCycles;
-  if (const char* e = getenv("SAGE_WAIT_LIMIT_US")) {
-    const long long us = atoll(e);
-    if (us > 0) p.wait_limit_cycles = us * 2000;        // ~2 GHz
-  }
-  p.test_drop_v_load = (getenv("SAGE_TEST_DROP_V_LOAD") != nullptr) ? 1 : 0;
+  // reports through `status`.  The failure-detection test shortens the bound and makes one wait run
+  // out on purpose through sage_test_set_wait_limit_us / sage_test_drop_v_load; the dropped load is
+  // only honoured together with a shortened bound.
+  const long long limit = g_wait_limit_cycles.load(std::memory_order_relaxed);
+  p.wait_limit_cycles = limit;
+  p.test_drop_v_load = (g_test_drop_v_load.load(std::memory_order_relaxed) != 0 && limit < sage::kWaitLimitCycles) ? 1 : 0;
 }
 
 int sm_count(int* out) {
-  static int cached[64] = {};
+  static std::atomic<int> cached[64];
   int dev = 0;
   SAGE_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && cached[dev] > 0) {
-    *out = cached[dev];
-    return SAGE_OK;
+  if (dev >= 0 && dev < 64) {
+    const int have = cached[dev].load(std::memory_order_relaxed);
+    if (have > 0) {
+      *out = have;
+      return SAGE_OK;
+    }
   }
   int sms = 0;
   SAGE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  if (dev >= 0 && dev < 64) cached[dev] = sms;
+  if (dev >= 0 && dev < 64) cached[dev].store(sms, std::memory_order_relaxed);
   *out = sms;
   return SAGE_OK;
+}
+
+// SAGE_STREAMK in the environment (read once): 0 turns the persistent launch off, 1 forces it.
+int streamk_override() {
+  static int value = -1;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* e = getenv("SAGE_STREAMK");
+    if (e != nullptr && (e[0] == '0' || e[0] == '1')) value = e[0] - '0';
+  });
+  return value;
 }
 
 // Persistent ("stream-K") scheduling.  The plain launch gives every CTA one whole item (a 128-row
@@ -192,9 +207,8 @@ struct StreamKPlan {
 int plan_streamk(StreamKPlan* plan, int B, int Hq, int Sq, int Skv, int D, int is_causal) {
   *plan = StreamKPlan();
   if (Sq <= 0 || Skv <= 0) return SAGE_OK;
-  if (const char* e = getenv("SAGE_STREAMK")) {
-    if (e[0] == '0') return SAGE_OK;                    // SAGE_STREAMK=0 turns the persistent launch off, =1 forces it
-  }
+  const int forced = streamk_override();
+  if (forced == 0) return SAGE_OK;
   int sms = 0;
   int rc = sm_count(&sms);
   if (rc) return rc;
@@ -229,7 +243,7 @@ int plan_streamk(StreamKPlan* plan, int B, int Hq, int Sq, int Skv, int D, int i
   // (1.04: the persistent CTAs of an SM run in lock-step, without the de-phasing yield of the plain launch)
   const double persistent = 1.04 * static_cast<double>(total) / grid + 5.0 + merge_steps;
   bool use = persistent < 0.95 * plain;
-  if (const char* e = getenv("SAGE_STREAMK")) use = (e[0] == '1') || use;
+  if (forced == 1) use = true;
   if (!use) return SAGE_OK;
   plan->use = true;
   plan->grid = static_cast<int>(grid);
@@ -240,13 +254,14 @@ int plan_streamk(StreamKPlan* plan, int B, int Hq, int Sq, int Skv, int D, int i
   return SAGE_OK;
 }
 
+// (Setting the attribute twice from two host threads that race on the first call is harmless.)
 template <typename Kernel>
-int configure_smem(Kernel kern, int smem_bytes, bool* configured) {
+int configure_smem(Kernel kern, int smem_bytes, std::atomic<bool>* configured) {
   int dev = 0;
   SAGE_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
+  if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
     SAGE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+    if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   return SAGE_OK;
 }
@@ -256,7 +271,7 @@ int launch_attn(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
                 const sage::AttnParams& p, cudaStream_t stream) {
   auto kern = sage::sage_attn_kernel<D, CAUSAL, DUMP, QKF, KST>;
   constexpr int kSmem = sage::AttnSmem<D, QKF ? 2 : 1, KST>::kTotal;
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64];
   int rc = configure_smem(kern, kSmem, configured);
   if (rc) return rc;
   const long long grid = static_cast<long long>(p.n_q_tiles) * p.B * p.Hq;
@@ -273,7 +288,7 @@ int launch_attn_streamk(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
                         sage::AttnParams p, const StreamKPlan& plan, void* workspace, cudaStream_t stream) {
   auto kern = sage::sage_attn_kernel<D, CAUSAL, false, QKF, 0, true>;
   constexpr int kSmem = sage::AttnSmem<D, QKF ? 2 : 1, 0>::kTotal;
-  static bool configured[64] = {};
+  static std::atomic<bool> configured[64];
   int rc = configure_smem(kern, kSmem, configured);
   if (rc) return rc;
   p.sk_total_tiles = plan.total_tiles;
@@ -320,6 +335,15 @@ extern "C" {
 
 int sage_abi_version(void) { return SAGE_ABI_VERSION; }
 const char* sage_last_error(void) { return g_err; }
+
+int sage_test_set_wait_limit_us(long long us) {
+  g_wait_limit_cycles.store(us > 0 ? us * 2000 : sage::kWaitLimitCycles, std::memory_order_relaxed);   // ~2 GHz
+  return SAGE_OK;
+}
+int sage_test_drop_v_load(int on) {
+  g_test_drop_v_load.store(on ? 1 : 0, std::memory_order_relaxed);
+  return SAGE_OK;
+}
 
 int sage_mean_seq(const sage_strided_t* k, int dtype, int B, int H, int S, int D, void* mean_out, void* stream) {
   SAGE_REQUIRE(k && k->ptr && mean_out, "sage_mean_seq: null pointer");

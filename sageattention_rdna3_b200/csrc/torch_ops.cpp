@@ -9,6 +9,8 @@
 #include <torch/library.h>
 #include <torch/types.h>
 
+#include <cuda_runtime.h>
+
 #include <vector>
 
 #include "../../include/sage_b200.h"
@@ -149,15 +151,16 @@ at::Tensor v_to_f16(const at::Tensor& v, int64_t layout) {
 }
 
 // qk_int8_sv_f16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor q_scale,
-//                     Tensor k_scale, int tensor_layout, int is_causal, float sm_scale,
-//                     Tensor? s_dump, Tensor? status, Tensor? lse) -> Tensor
-// Counterpart of qk_int8_sv_bf16_attn_t (csrc/pybind_gfx11.cpp:19-23): query/key are the int8
-// [B,H,S,D] tensors from quant_qk_int8; `value` is fp16 in `value_layout`; `output` is fp16/bf16 in
+//                     Tensor k_scale, int tensor_layout, int is_causal, float sm_scale, *,
+//                     int value_layout=-1, Tensor? s_dump, Tensor? status, Tensor? lse) -> Tensor
+// Counterpart of qk_int8_sv_bf16_attn_t (csrc/pybind_gfx11.cpp:19-23), call-compatible with its nine
+// positional arguments: query/key are the int8 [B,H,S,D] tensors from quant_qk_int8; `value` is fp16
+// in `value_layout` (keyword; -1 = the same as `tensor_layout`); `output` is fp16/bf16 in
 // `tensor_layout`.  sm_scale is already folded into q_scale and is accepted for signature parity.
 // `lse` (optional, fp32 [B,Hq,Sq]) receives the natural-log sum of exponentials of every row.
 at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, const at::Tensor& v, at::Tensor& o,
                                const at::Tensor& q_scale, const at::Tensor& k_scale, int64_t layout,
-                               int64_t value_layout, int64_t is_causal, double /*sm_scale*/,
+                               int64_t is_causal, double /*sm_scale*/, int64_t value_layout,
                                const c10::optional<at::Tensor>& s_dump, const c10::optional<at::Tensor>& status,
                                const c10::optional<at::Tensor>& lse) {
   TORCH_CHECK(q_i8.is_cuda() && q_i8.scalar_type() == at::kChar && q_i8.is_contiguous() && q_i8.dim() == 4,
@@ -167,6 +170,7 @@ at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, c
   TORCH_CHECK(v.scalar_type() == at::kHalf, "value must be fp16 (convert bf16 with v_to_f16 / prep_qkv)");
   check_16b(v, "value");
   check_16b(o, "output");
+  if (value_layout < 0) value_layout = layout;
   const int64_t B = q_i8.size(0), Hq = q_i8.size(1), Sq = q_i8.size(2), D = q_i8.size(3);
   const int64_t Hkv = k_i8.size(1), Skv = k_i8.size(2);
   const Dims dv = dims_of(v, value_layout), d_o = dims_of(o, layout);
@@ -279,9 +283,31 @@ at::Tensor bf16_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor&
 // fp16_attn / bf16_attn) or the INT8 branch (:165-198: [mean,] quantise, attention).  Returns
 // [output] or, with smooth_k on the INT8 branch, [output, key_mean] (the caller needs the mean to
 // refer a log-sum-exp to the original keys).  One Python -> C++ crossing instead of two to four.
+// `status_host` (optional, one pinned int32): the status word is copied there behind the kernels, so
+// the caller can look at it later without synchronising.
+std::vector<at::Tensor> sageattn_fwd_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
+                                          int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
+                                          const at::Tensor& status, const c10::optional<at::Tensor>& lse);
+
 std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
                                      int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
-                                     const at::Tensor& status, const c10::optional<at::Tensor>& lse) {
+                                     const at::Tensor& status, const c10::optional<at::Tensor>& lse,
+                                     const c10::optional<at::Tensor>& status_host) {
+  std::vector<at::Tensor> out = sageattn_fwd_impl(q, k, v, layout, is_causal, sm_scale, smooth_k, use_direct, status, lse);
+  if (status_host.has_value()) {
+    TORCH_CHECK(status_host->is_pinned() && status_host->scalar_type() == at::kInt && status_host->numel() >= 1,
+                "status_host must be a pinned int32 host tensor");
+    c10::cuda::CUDAGuard guard(q.device());
+    const cudaError_t e = cudaMemcpyAsync(status_host->data_ptr(), status.data_ptr(), sizeof(int), cudaMemcpyDeviceToHost,
+                                          static_cast<cudaStream_t>(current_stream(q)));
+    TORCH_CHECK(e == cudaSuccess, "copy of the status word failed: ", cudaGetErrorString(e));
+  }
+  return out;
+}
+
+std::vector<at::Tensor> sageattn_fwd_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
+                                          int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
+                                          const at::Tensor& status, const c10::optional<at::Tensor>& lse) {
   at::Tensor o = at::empty_like(q);
   const bool bf16 = q.scalar_type() == at::kBFloat16;
   const c10::optional<at::Tensor> st(status), none;
@@ -295,8 +321,8 @@ std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, c
   }
   at::Tensor k_mean = smooth_k ? mean_seq(k, layout) : at::empty({0}, q.options());
   std::vector<at::Tensor> parts = quant_impl(q, k, k_mean, bf16 ? &v : nullptr, layout, sm_scale);
-  qk_int8_sv_f16_attn(parts[0], parts[2], bf16 ? parts[4] : v, o, parts[1], parts[3], layout, bf16 ? kHND : layout,
-                      is_causal, sm_scale, none, st, lse);
+  qk_int8_sv_f16_attn(parts[0], parts[2], bf16 ? parts[4] : v, o, parts[1], parts[3], layout, is_causal, sm_scale,
+                      bf16 ? kHND : layout, none, st, lse);
   if (smooth_k) return {o, k_mean};
   return {o};
 }
@@ -305,13 +331,13 @@ std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, c
 
 TORCH_LIBRARY(sageattention, m) {
   m.def("sageattn_fwd(Tensor query, Tensor key, Tensor value, int tensor_layout, int is_causal, float sm_scale, "
-        "int smooth_k, int use_direct, Tensor status, Tensor? lse=None) -> Tensor[]");
+        "int smooth_k, int use_direct, Tensor status, Tensor? lse=None, Tensor? status_host=None) -> Tensor[]");
   m.def("fp16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
         "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("bf16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
         "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("qk_int8_sv_f16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor q_scale, "
-        "Tensor k_scale, int tensor_layout, int value_layout, int is_causal, float sm_scale, "
+        "Tensor k_scale, int tensor_layout, int is_causal, float sm_scale, *, int value_layout=-1, "
         "Tensor? s_dump=None, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("quant_qk_int8(Tensor query, Tensor key, Tensor key_mean, int tensor_layout, float sm_scale) -> Tensor[]");
   m.def("prep_qkv(Tensor query, Tensor key, Tensor value, Tensor key_mean, int tensor_layout, float sm_scale) "

@@ -1,11 +1,11 @@
 """``sageattn`` for inputs that live in (pinned) host memory.
 
-A call with host buffers is bound by PCIe: for BASELINE config 3 the kernels take about 1 ms and
+A call with host buffers is bound by PCIe: for B=2 H=32 S=8192 D=128 the kernels take about 1 ms and
 the copies about 10.  ``sageattn_host`` cuts q, k, v into chunks of whole (batch, kv-head) units -
 each an independent attention problem - and runs them through three CUDA streams: chunk i+1 is
 copied in while chunk i is computed and chunk i-1 is copied back, so the two PCIe directions and
 the GPU overlap.  The results are those of one ``sageattn`` call on device tensors (bit for bit
-when both take the same launch schedule).  16 chunks measured best for config 3 (8.1 ms against
+when both take the same launch schedule).  16 chunks measured best for that shape (8.1 ms against
 8.4 with 8 and 9.1 with 32: finer chunks shorten the fill and drain of the pipeline until the host
 side of the per-chunk calls shows).
 """
@@ -28,10 +28,14 @@ def _unit_chunks(batch: int, hkv: int, rep: int, want: int) -> List[Tuple[int, i
 def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
                   tensor_layout: str = "HND", is_causal: bool = False, sm_scale: Optional[float] = None,
                   smooth_k: bool = False, device: Optional[torch.device] = None, chunks: int = 16,
-                  **kwargs) -> torch.Tensor:
+                  wait: bool = True, **kwargs):
     """q, k, v: CPU tensors (pinned memory for asynchronous copies) in ``tensor_layout``; returns a
     pinned CPU tensor shaped like q (or fills ``out``).  With "HND" the work is cut along batch and
-    heads; "NHD" head slices are not contiguous in host memory, so it is cut along the batch only."""
+    heads; "NHD" head slices are not contiguous in host memory, so it is cut along the batch only.
+
+    With ``wait=True`` (default) the call returns once the last device-to-host copy has finished:
+    the returned tensor can be read at once.  ``wait=False`` returns ``(out, event)`` straight after
+    the work is enqueued; ``out`` holds the result only after ``event.synchronize()``."""
     assert not q.is_cuda and not k.is_cuda and not v.is_cuda, "sageattn_host takes host tensors"
     assert tensor_layout in ("HND", "NHD")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -88,6 +92,11 @@ def sageattn_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Option
     for t in (qd_all, kd_all, vd_all):
         t.record_stream(s_in)
         t.record_stream(s_run)
+    last = done_events[-1] if done_events else None
+    if not wait:
+        return out, last
+    if last is not None:
+        last.synchronize()        # copies on s_out complete in order: the last one covers them all
     return out
 
 

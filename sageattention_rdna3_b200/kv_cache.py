@@ -45,7 +45,12 @@ class QuantizedKV:
 
 
 def quantize_kv(k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND", smooth_k: bool = False) -> QuantizedKV:
-    """The K/V half of ``sageattn``'s INT8 path: [K mean] and one quantisation launch."""
+    """The K/V half of ``sageattn``'s INT8 path: [K mean] and one quantisation launch.
+
+    The int8 keys, their scales and the mean are snapshots.  The values are a snapshot only for bf16
+    inputs (an fp16 copy is made); for fp16 inputs ``v16`` IS the caller's ``v``, not a copy: writing
+    into ``v`` afterwards changes what later ``sageattn_quantized_kv`` calls read while the keys stay
+    as they were.  Pass ``v.clone()`` if the tensor will be reused."""
     assert k.is_cuda and v.is_cuda and k.device == v.device, "k, v must be CUDA tensors on one device."
     assert k.dtype == v.dtype and k.dtype in (torch.float16, torch.bfloat16), "k, v must both be fp16 or bf16."
     assert tensor_layout in _LAYOUT_CODE, f"tensor_layout must be 'HND' or 'NHD', got {tensor_layout!r}."
@@ -110,8 +115,8 @@ def sageattn_quantized_kv(q: torch.Tensor, kv: QuantizedKV, is_causal: bool = Fa
         shape[seq_dim], shape[head_idx] = 0, kv.num_kv_heads
         no_k = q.new_empty(shape)           # an empty key: only the Q blocks of the launch exist
         q_int8, q_scale, _, _ = ops.quant_qk_int8(q, no_k, q.new_empty(0), layout, sm_scale)
-        ops.qk_int8_sv_f16_attn(q_int8, kv.k_int8, kv.v16, o, q_scale, kv.k_scale, layout, kv.v_layout,
-                                int(is_causal), sm_scale, None, _status_word(q.device), lse)
+        ops.qk_int8_sv_f16_attn(q_int8, kv.k_int8, kv.v16, o, q_scale, kv.k_scale, layout, int(is_causal), sm_scale,
+                                value_layout=kv.v_layout, status=_status_word(q.device), lse=lse)
         if return_lse and kv.k_mean is not None:
             km = kv.k_mean.float().repeat_interleave(Hq // kv.num_kv_heads, dim=1)
             eq = "bhsd,bhd->bhs" if tensor_layout == "HND" else "bshd,bhd->bhs"

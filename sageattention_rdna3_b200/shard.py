@@ -72,12 +72,17 @@ def from_units(o_units: torch.Tensor, batch: int, num_qo_heads: int, tensor_layo
 
 def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                      is_causal: bool = False, sm_scale: Optional[float] = None, smooth_k: bool = False,
-                     group=None, gather: bool = True, attn_fn: Optional[Callable] = None, **kwargs):
+                     group=None, gather: bool = True, attn_fn: Optional[Callable] = None,
+                     global_heads: Optional[tuple] = None, **kwargs):
     """Run this rank's share of ``sageattn(q, k, v)`` and optionally all-gather the outputs.
 
-    Every rank passes the same global ``q, k, v`` (or at least its own units filled in).  Returns the
-    full output in the caller's layout when ``gather`` is true, otherwise this rank's units
-    ``[n, Hq/Hkv, Sq, D]`` and its :class:`Shard`.  ``attn_fn`` defaults to :func:`sageattn`; other
+    Two ways to pass the inputs.  Global: every rank passes the same global ``q, k, v`` in
+    ``tensor_layout`` (or at least its own units filled in).  Rank-local: with
+    ``global_heads=(B, Hq, Hkv)`` of the whole problem, ``q, k, v`` are only this rank's units of
+    :func:`plan_shards`, already in unit form - q ``[n, Hq/Hkv, Sq, D]``, k and v ``[n, 1, Skv, D]`` -
+    so no rank ever holds another rank's data; ``tensor_layout`` then only names the layout of the
+    gathered result.  Returns the full output in ``tensor_layout`` when ``gather`` is true,
+    otherwise this rank's units ``[n, Hq/Hkv, Sq, D]`` and its :class:`Shard`.  ``attn_fn`` defaults to :func:`sageattn`; other
     keyword arguments go to it.  The choice between the INT8 and the un-quantised kernel is made
     here, from the caller's shapes and layout, so that every rank and the unsharded call agree.
     """
@@ -86,16 +91,28 @@ def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_l
         from .core import sageattn as attn_fn
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
-    B = q.size(0)
-    hq = q.size(1) if tensor_layout == "HND" else q.size(2)
-    hkv = k.size(1) if tensor_layout == "HND" else k.size(2)
-    shards = plan_shards(B, hq, hkv, world)
-    mine = shards[rank]
-    ql, kl, vl = shard_inputs(q, k, v, tensor_layout, mine)
+    if global_heads is not None:
+        B, hq, hkv = global_heads
+        shards = plan_shards(B, hq, hkv, world)
+        mine = shards[rank]
+        if q.size(0) != mine.n_units or q.size(1) != hq // hkv or k.size(1) != 1:
+            raise ValueError(f"rank {rank} owns {mine.n_units} units of {hq // hkv} query head(s): expected q "
+                             f"[{mine.n_units}, {hq // hkv}, Sq, D] and k, v [{mine.n_units}, 1, Skv, D], got "
+                             f"{tuple(q.shape)} and {tuple(k.shape)}")
+        ql, kl, vl = q, k, v
+        q_len, kv_len = q.size(2), k.size(2)
+    else:
+        B = q.size(0)
+        hq = q.size(1) if tensor_layout == "HND" else q.size(2)
+        hkv = k.size(1) if tensor_layout == "HND" else k.size(2)
+        shards = plan_shards(B, hq, hkv, world)
+        mine = shards[rank]
+        ql, kl, vl = shard_inputs(q, k, v, tensor_layout, mine)
+        s_dim = 2 if tensor_layout == "HND" else 1
+        q_len, kv_len = q.size(s_dim), k.size(s_dim)
     if "kernel" not in kwargs:
         from .core import use_direct_kernel
-        s_dim = 2 if tensor_layout == "HND" else 1
-        direct = use_direct_kernel(q.size(-1), tensor_layout, is_causal, q.size(s_dim), k.size(s_dim))
+        direct = use_direct_kernel(q.size(-1), tensor_layout, is_causal, q_len, kv_len)
         kwargs["kernel"] = "direct" if direct else "int8"
     if mine.n_units > 0:
         o_local = attn_fn(ql, kl, vl, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k,

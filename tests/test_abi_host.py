@@ -25,7 +25,8 @@ def test_header_declares_the_expected_entry_points():
                                          "sage_quant_qk_int8", "sage_v_to_f16", "sage_qk_int8_sv_f16_attn",
                                          "sage_qk_int8_sv_f16_attn_lse", "sage_direct_attn", "sage_attn_workspace_bytes",
                                          "sage_qk_int8_sv_f16_attn_ws", "sage_direct_attn_ws",
-                                         "sage_quant_qk_int8_smooth_static"])
+                                         "sage_quant_qk_int8_smooth_static", "sage_test_set_wait_limit_us",
+                                         "sage_test_drop_v_load"])
 
 
 def test_library_exports_every_declared_symbol():

@@ -44,6 +44,13 @@ def _worker(rank, world, port, layout, B, Hq, Hkv, kernel, result_dir):
         out = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, attn_fn=_oracle_attn, **kw)
         local, shard = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True,
                                         attn_fn=_oracle_attn, gather=False, **kw)
+        # rank-local form: the rank passes only its own units and the head counts of the whole problem
+        from sageattention_rdna3_b200.shard import shard_inputs
+        ql, kl, vl = shard_inputs(q, k, v, layout, shard)
+        kw_local = dict(kw) if kw else {"kernel": "direct"}
+        out_local = sageattn_sharded(ql, kl, vl, tensor_layout=layout, is_causal=True, smooth_k=True,
+                                     attn_fn=_oracle_attn, global_heads=(B, Hq, Hkv), **kw_local)
+        assert torch.equal(out_local, out), "rank-local inputs give a different gathered output"
         torch.save({"out": out, "n_local": shard.n_units, "local_shape": tuple(local.shape)},
                    os.path.join(result_dir, f"rank{rank}.pt"))
     finally:

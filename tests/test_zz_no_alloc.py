@@ -39,8 +39,12 @@ def _static_quant(q, k, layout, sm_scale):
 
 
 @pytest.mark.gpu
-def test_static_entry_point_matches_allocating_path_twice_in_a_row():
-    dev = torch.device("cuda", 0)
+@pytest.mark.parametrize("index", [0, 1])
+def test_static_entry_point_matches_allocating_path_twice_in_a_row(index):
+    if index >= torch.cuda.device_count():
+        pytest.skip("the buffer's address is looked up per device: the second device needs a second GPU")
+    dev = torch.device("cuda", index)
+    torch.cuda.set_device(dev)
     calls = [
         # B, Hq, Hkv, Sq, Skv, D, dtype, layout, K offset
         (2, 8, 4, 700, 700, 128, torch.bfloat16, "HND", 3.0),     # fills 1024 elements of the buffer
@@ -54,6 +58,21 @@ def test_static_entry_point_matches_allocating_path_twice_in_a_row():
         want = H.abi_quant(q, k, H.abi_mean_seq(k, layout), layout, sm)[:4]
         got = _static_quant(q, k, layout, sm)
         torch.cuda.synchronize()
+        if n > 0:
+            # The property in the name: after the first call on the device (which looks the buffer's
+            # address up) a call must leave the device's free memory and torch's allocator untouched.
+            # _static_quant allocates the OUTPUTS, so call the entry point once more on the same ones.
+            lib = _native.load_abi()
+            qs, ks = H.strided(q, layout), H.strided(k, layout)
+            free_before, allocated_before = torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev)
+            rc = lib.sage_quant_qk_int8_smooth_static(
+                ctypes.byref(qs), ctypes.byref(ks), H.dtype_code(q), B, Hq, Hkv, Sq, Skv, D, float(sm),
+                got[0].data_ptr(), got[1].data_ptr(), got[2].data_ptr(), got[3].data_ptr(),
+                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            assert rc == 0
+            assert torch.cuda.mem_get_info(dev)[0] == free_before, "the call changed the device's free memory"
+            assert torch.cuda.memory_allocated(dev) == allocated_before
         for name, a, b in zip(("q_i8", "q_scale", "k_i8", "k_scale"), got, want):
             if a.dtype == torch.float32:
                 assert torch.equal(a.view(torch.int32), b.view(torch.int32)), f"call {n}: {name} differs"
