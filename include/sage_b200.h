@@ -59,6 +59,13 @@ const char* sage_last_error(void);
 int sage_test_set_wait_limit_us(long long us);
 int sage_test_drop_v_load(int on);
 
+/* Launch schedule of the attention entry points that take a workspace: -1 = the library's cost
+ * model decides between one CTA per query tile and persistent CTAs (default), 0 = never
+ * persistent, 1 = always.  Process-wide; the environment variable SAGE_STREAMK=0|1, read once at
+ * the first launch, sets the initial value.  Takes the place of the reference's per-launch
+ * environment overrides of its tile choice (csrc/attn_gfx11.cu:2101-2114). */
+int sage_set_streamk(int mode);
+
 /* Mean of K over the sequence, per (batch, head, channel), in the input dtype.
  * Replaces mean_seq_gfx11 (csrc/attn_gfx11.h:48; csrc/attn_gfx11.cu:1937-1972, kernel :94-145):
  * same fp32 summation order (256 strided partial sums, added serially), one fp32 division, one

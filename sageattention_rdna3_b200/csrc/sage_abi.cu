@@ -177,15 +177,20 @@ int sm_count(int* out) {
   return SAGE_OK;
 }
 
-// SAGE_STREAMK in the environment (read once): 0 turns the persistent launch off, 1 forces it.
+// Choice between the plain and the persistent launch: -1 = by the cost model, 0 = never persistent,
+// 1 = always.  SAGE_STREAMK in the environment (read once, at the first use) gives the initial
+// value; sage_set_streamk changes it afterwards.
+std::atomic<int> g_streamk_mode{-2};      // -2: environment not looked at yet
 int streamk_override() {
-  static int value = -1;
   static std::once_flag once;
   std::call_once(once, [] {
+    int value = -1;
     const char* e = getenv("SAGE_STREAMK");
     if (e != nullptr && (e[0] == '0' || e[0] == '1')) value = e[0] - '0';
+    int expected = -2;
+    g_streamk_mode.compare_exchange_strong(expected, value);
   });
-  return value;
+  return g_streamk_mode.load(std::memory_order_relaxed);
 }
 
 // Persistent ("stream-K") scheduling.  The plain launch gives every CTA one whole item (a 128-row
@@ -338,6 +343,12 @@ const char* sage_last_error(void) { return g_err; }
 
 int sage_test_set_wait_limit_us(long long us) {
   g_wait_limit_cycles.store(us > 0 ? us * 2000 : sage::kWaitLimitCycles, std::memory_order_relaxed);   // ~2 GHz
+  return SAGE_OK;
+}
+int sage_set_streamk(int mode) {
+  if (mode < -1 || mode > 1) return fail(SAGE_ERR_INVALID, "sage_set_streamk: mode must be -1 (auto), 0 (off) or 1 (on)");
+  streamk_override();                     // settle the environment's value first, so that it cannot overwrite this one
+  g_streamk_mode.store(mode, std::memory_order_relaxed);
   return SAGE_OK;
 }
 int sage_test_drop_v_load(int on) {

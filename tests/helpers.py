@@ -102,3 +102,8 @@ def abi_attn(q_i8, k_i8, v16, v_layout, q_scale, k_scale, out_dtype, out_layout,
            "sage_qk_int8_sv_f16_attn")
     torch.cuda.synchronize()
     return o, s_dump, int(status.item())
+
+
+def set_streamk(mode):
+    """Launch schedule of the attention kernels: -1 cost model, 0 plain, 1 persistent (sage_set_streamk)."""
+    assert _native.load_abi().sage_set_streamk(int(mode)) == 0

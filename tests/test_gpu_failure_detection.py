@@ -74,7 +74,7 @@ def test_later_ctas_leave_at_once_when_the_status_word_is_set(hooks):
     t0 = time.perf_counter()
     _, _, status = H.abi_attn(q_i8, k_i8, vd, "HND", q_scale, k_scale, torch.float16, "HND", False)
     dt = time.perf_counter() - t0
-    assert status == 2 + 16 * 6
+    assert status % 16 == 2, status      # some bounded wait gave up (which one reports first is a race)
     assert dt < 0.15, f"a failing launch of 3.5 waves took {dt * 1e3:.0f} ms with a 50 ms bound"
 
 
