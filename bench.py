@@ -3,15 +3,15 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C3] [--impl reference]
 
-One "step" is one pass of the hot path (K mean when smooth_k, Q/K quantisation + fp16 copy of V,
-fused attention) over one batch of synthetic input of the named workload.  One JSON line is printed:
+One "step" is one pass of the hot path (Q/K quantisation, with the K mean when smooth_k, + fp16 copy
+of V; fused attention) over one batch of synthetic input of the named workload.  One JSON line is printed:
 
 * ``value``     - attention TOPS, 4*B*Hq*Sq*Skv*D / t (benchmark_attn/benchmark_attn.py:40-47 of the
                   reference), timed through ``sageattn()`` on inputs resident in HBM, aggregated over
                   all ranks (time = max over ranks).
 * ``roofline``  - the fused attention kernel against the tensor-core roofline (executed flops, burst
                   peak), from a second loop that calls the operators with events around each kernel;
-                  ``roofline_prep`` / ``roofline_kmean`` give the two HBM-bound kernels.
+                  ``roofline_prep`` gives the HBM-bound preparation kernel.
 * ``e2e``       - the same metric through ``sageattn_host()`` with HOST (pinned) q, k, v and a host
                   output: the copies in both directions are inside the timed region; ``copy_floor_ms``
                   is the same bytes copied with no compute.
@@ -250,8 +250,10 @@ class Problem:
         self.o = torch.empty_like(self.q)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.empty_mean = torch.empty(0, device=dev, dtype=self.q.dtype)
-        self.attn_events, self.prep_events, self.mean_events = [], [], []
-        self.launches_per_step = 2 + (1 if w["smooth_k"] else 0)
+        self.attn_events, self.prep_events = [], []
+        # the same choice sageattn() makes: one preparation launch for few heads, K mean + preparation otherwise
+        self.fused_prep = bool(w["smooth_k"] and lib.sage_prep_smooth_preferred(self.Bl, self.Hkvl))
+        self.launches_per_step = 2 + (1 if (w["smooth_k"] and not self.fused_prep) else 0)
         # a problem that fills the GPU unevenly runs on persistent CTAs and adds the merge kernel
         if lib.sage_attn_workspace_bytes(self.Bl, self.Hql, w["S"], w["S"], w["D"], int(w["causal"])) > 0:
             self.launches_per_step += 1
@@ -266,18 +268,22 @@ class Problem:
         """The hot path as its operators, optionally with CUDA events around each kernel."""
         w, ops = self.w, self.ops
         o = self.o if o is None else o
-        m0 = self._ev() if record else None
-        k_mean = ops.mean_seq(self.k, self.layout_code) if w["smooth_k"] else self.empty_mean
+        bf16 = self.q.dtype == torch.bfloat16
         p0 = self._ev() if record else None
-        if self.q.dtype == torch.bfloat16:
-            q8, qs, k8, ks, v16 = ops.prep_qkv(self.q, self.k, self.v, k_mean, self.layout_code, self.sm_scale)
-            vl = 1
+        if w["smooth_k"] and self.fused_prep:       # few heads: K mean and quantisation in one launch
+            parts = ops.prep_smooth_qkv(self.q, self.k, self.v if bf16 else None, self.layout_code, self.sm_scale)
+            q8, qs, k8, ks = parts[:4]
+            v16, vl = (parts[5], 1) if bf16 else (self.v, self.layout_code)
         else:
-            q8, qs, k8, ks = ops.quant_qk_int8(self.q, self.k, k_mean, self.layout_code, self.sm_scale)
-            v16, vl = self.v, self.layout_code
+            k_mean = ops.mean_seq(self.k, self.layout_code) if w["smooth_k"] else self.empty_mean
+            if bf16:
+                q8, qs, k8, ks, v16 = ops.prep_qkv(self.q, self.k, self.v, k_mean, self.layout_code, self.sm_scale)
+                vl = 1
+            else:
+                q8, qs, k8, ks = ops.quant_qk_int8(self.q, self.k, k_mean, self.layout_code, self.sm_scale)
+                v16, vl = self.v, self.layout_code
         if record:
             e0 = self._ev()
-            self.mean_events.append((m0, p0))
             self.prep_events.append((p0, e0))
         ops.qk_int8_sv_f16_attn(q8, k8, v16, o, qs, ks, self.layout_code, int(w["causal"]), self.sm_scale,
                                 value_layout=vl, status=self.status)
@@ -294,16 +300,17 @@ class Problem:
 
     def kernel_ms(self):
         avg = lambda evs: sum(a.elapsed_time(b) for a, b in evs) / max(len(evs), 1)
-        return avg(self.attn_events), avg(self.prep_events), avg(self.mean_events)
+        return avg(self.attn_events), avg(self.prep_events)
 
     def hbm_bytes(self):
-        """Algorithmic bytes of the two HBM-bound kernels on this rank."""
+        """Algorithmic bytes of the preparation launch on this rank (with smooth_k it includes the mean)."""
         w, e = self.w, self.q.element_size()
         nq, nk = self.q.numel(), self.k.numel()
         n_scales = self.Bl * self.Hql * ((w["S"] + 31) // 32) + self.Bl * self.Hkvl * ((w["S"] + 15) // 16)
         prep = nq * e + nk * e + nq + nk + 4 * n_scales + (nk * (e + 2) if self.q.dtype == torch.bfloat16 else 0)
-        mean = nk * e + self.Bl * self.Hkvl * w["D"] * e
-        return prep, mean
+        if w["smooth_k"]:
+            prep += self.Bl * self.Hkvl * w["D"] * e
+        return prep
 
 
 def timed(fn, steps, barrier):
@@ -437,7 +444,7 @@ def measure_e2e(prob, steps, barrier):
     return {"ms": ms, "copy_floor_ms": floor, "h2d": h2d, "d2h": d2h}
 
 
-def roofline_records(prob, attn_ms, prep_ms, mean_ms, peaks, capped):
+def roofline_records(prob, attn_ms, prep_ms, peaks, capped):
     """Roofline objects of the three kernels from their event-timed launches on this rank."""
     w = prob.w
     # Half of the executed operations are int8 (QK^T, taken as 2x the bf16 rate), half fp16 (PV):
@@ -456,16 +463,13 @@ def roofline_records(prob, attn_ms, prep_ms, mean_ms, peaks, capped):
         "frac_of_sustained_peak": achieved / peak_sustained, "power_capped_during_run": capped,
         "peak_source": f"{peaks['source']}: cuBLAS bf16 {peaks['bf16_tflops']} TFLOP/s (burst), int8 taken as 2x; "
                        "executed flops, half int8 half fp16"}}
-    prep_bytes, mean_bytes = prob.hbm_bytes()
-    out["roofline_prep"] = {"bound": "hbm", "kernel": "sage_prep_kernel", "achieved": prep_bytes / (prep_ms / 1e3) / 1e9,
-                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
+    prep_bytes = prob.hbm_bytes()
+    kernel = "sage_prep_kernel" if not w["smooth_k"] else \
+        ("sage_prep_smooth_kernel" if prob.fused_prep else "sage_kmean_kernel + sage_prep_kernel (K is read twice)")
+    out["roofline_prep"] = {"bound": "hbm", "kernel": kernel,
+                            "achieved": prep_bytes / (prep_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": prep_bytes / (prep_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "ms_per_launch": prep_ms,
                             "bytes": prep_bytes}
-    if w["smooth_k"] and mean_ms > 0:
-        out["roofline_kmean"] = {"bound": "hbm", "kernel": "sage_kmean_kernel",
-                                 "achieved": mean_bytes / (mean_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                 "frac": mean_bytes / (mean_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "ms_per_launch": mean_ms,
-                                 "bytes": mean_bytes}
     return out
 
 
@@ -477,7 +481,7 @@ def run_extra_config(name, dev, ops, lib, peaks, steps=10, warmup=3):
     for _ in range(warmup):
         prob.step_ops()
     ms = timed(lambda i: prob.step_ops(record=True), steps, torch.cuda.synchronize)
-    attn_ms, prep_ms, _ = prob.kernel_ms()
+    attn_ms, prep_ms = prob.kernel_ms()
     achieved = prob.executed / (attn_ms / 1e3) / 1e12
     return {"workload": workload_string(name, w), "ms_per_step": ms, "tops": prob.nominal / (ms / 1e3) / 1e12,
             "attn_ms": attn_ms, "prep_ms": prep_ms, "attn_executed_tflops": achieved,
@@ -549,7 +553,7 @@ def main():
         for _ in range(args.warmup):
             prob.step_ops()
         ms_ops = timed(lambda i: prob.step_ops(record=True), args.steps, barrier)
-        attn_ms, prep_ms, mean_ms = prob.kernel_ms()
+        attn_ms, prep_ms = prob.kernel_ms()
         # (3) with the final all-gather of the outputs
         if world > 1 and strong and not args.no_gather:
             gather = measure_gather(prob, args.steps, args.warmup, barrier, world, dist, sizes)
@@ -589,12 +593,12 @@ def main():
             "timed_call": "sageattn(q, k, v, kernel='int8') on HBM-resident inputs, max over ranks",
             "executed_tops": total_executed / (ms_public / 1e3) / 1e12,
             "operator_loop": {"ms_per_step": ms_ops, "value": tops(ms_ops),
-                              "note": "the same step as mean_seq / prep_qkv / qk_int8_sv_f16_attn with events around "
-                                      "each kernel; the rooflines come from it"},
+                              "note": "the same step as its two operators (preparation, attention) with events "
+                                      "around each kernel; the rooflines come from it"},
             "gpu_launches": prob.launches_per_step * args.steps,
             "clocks": clocks,
         }
-        line.update(roofline_records(prob, attn_ms, prep_ms, mean_ms, peaks, capped))
+        line.update(roofline_records(prob, attn_ms, prep_ms, peaks, capped))
         if gather:
             recv = gather["recv_bytes_per_rank"]
             line["allgather"] = {

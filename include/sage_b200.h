@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SAGE_ABI_VERSION 4
+#define SAGE_ABI_VERSION 5
 
 #define SAGE_DTYPE_F16 0
 #define SAGE_DTYPE_BF16 1
@@ -159,6 +159,22 @@ int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const 
                         int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status,
                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* smooth_k preparation in ONE launch: the K mean, K quantised against it, Q quantised, and (if `v` and
+ * `v16` are non-NULL) the fp16 copy of V.  Replaces the sequence mean_seq_gfx11 -> quant_qk_int8_gfx11
+ * (-> v_transpose_gfx11) that sageattention/core.py:186-193 issues for smooth_k=True
+ * (csrc/attn_gfx11.h:41-48; kernels csrc/attn_gfx11.cu:94-145, :147-321): same arithmetic and summation
+ * order, bit-identical outputs, but K is read from DRAM once - the cluster of CTAs that has summed a
+ * (batch, kv-head) quantises it while it is still in L2.  k_mean_out: [B,Hkv,D], input dtype.
+ * Skv must be >= 1; other arguments as for sage_quant_qk_int8. */
+int sage_prep_smooth_qkv(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v, void* v16, int dtype,
+                         int B, int Hq, int Hkv, int Sq, int Skv, int D, float sm_scale, int8_t* q_i8, float* q_scale,
+                         int8_t* k_i8, float* k_scale, void* k_mean_out, void* stream);
+/* 1 if sage_prep_smooth_qkv is the faster way to prepare B * Hkv (batch, kv-head) pairs on the current
+ * device, 0 if sage_mean_seq followed by sage_quant_qk_int8 is (many heads: measured on B200, the
+ * one-launch form wins up to about SMs / 8 pairs).  Same results either way.  No counterpart in the
+ * reference (its launch sequence is fixed, sageattention/core.py:186-193). */
+int sage_prep_smooth_preferred(int B, int Hkv);
+
 /* Smooth-K quantisation for callers that must not allocate device memory.
  * No counterpart in the reference (its launchers allocate through torch).
  *
@@ -186,6 +202,18 @@ int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const 
 int sage_quant_qk_int8_smooth_static(const sage_strided_t* q, const sage_strided_t* k, int dtype, int B, int Hq,
                                      int Hkv, int Sq, int Skv, int D, float sm_scale, int8_t* q_i8, float* q_scale,
                                      int8_t* k_i8, float* k_scale, void* stream);
+
+/* Fold one partial attention result into running accumulators - the merge step of attention over a
+ * sequence that is split across GPUs (each partial covers a disjoint set of keys):
+ *   lse' = log(exp(lse) + exp(lse_j)),  o' = o * exp(lse - lse') + o_j * exp(lse_j - lse').
+ * o_acc: fp32 [B,H,S,D] described by element strides (32-byte aligned base); lse_acc: fp32 rows of
+ * length S at lse_acc + b * lse_stride_b + h * lse_stride_h; o_part: the partial output (f16 / bf16)
+ * as the attention entry points write it; lse_part: fp32 [B,H,S] contiguous, as they return it.
+ * first != 0: the accumulators are overwritten instead of read.  No counterpart in the reference,
+ * whose `return_lse` is a placeholder (sageattention/core.py:203-211). */
+int sage_fold_attn_partial(const sage_strided_t* o_acc, float* lse_acc, int64_t lse_stride_b, int64_t lse_stride_h,
+                           const sage_strided_t* o_part, int part_dtype, const float* lse_part, int B, int H, int S, int D,
+                           int first, void* stream);
 
 #ifdef __cplusplus
 }

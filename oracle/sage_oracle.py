@@ -287,6 +287,28 @@ def sdpa_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: 
     return o
 
 
+def fold_partial(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_j: torch.Tensor, lse_j: torch.Tensor,
+                 tensor_layout: str, first: bool) -> None:
+    """Checker for the fold of partial attention results (sage_fold_attn_partial), in place on fp32
+    accumulators: lse' = logaddexp(lse, lse_j); o' = o * exp(lse - lse') + o_j * exp(lse_j - lse').
+    The reference has no counterpart; its ``return_lse`` is a placeholder (sageattention/core.py:203-211)."""
+    o_j = o_j.float()
+    if first:
+        o_acc.copy_(o_j)
+        lse_acc.copy_(lse_j)
+        return
+    new = torch.logaddexp(lse_acc, lse_j)
+    # a row that has seen no key on either side has -inf twice: exp(nan) -> weight 0
+    w_old = torch.nan_to_num(torch.exp(lse_acc - new), nan=0.0)
+    w_new = torch.nan_to_num(torch.exp(lse_j - new), nan=0.0)
+    if tensor_layout == "HND":
+        w_old, w_new = w_old[..., None], w_new[..., None]                       # [B,H,S,1]
+    else:
+        w_old, w_new = w_old.transpose(1, 2)[..., None], w_new.transpose(1, 2)[..., None]   # [B,S,H,1]
+    o_acc.copy_(o_acc * w_old + o_j * w_new)
+    lse_acc.copy_(new)
+
+
 def accuracy(a: torch.Tensor, b: torch.Tensor) -> dict:
     """Cosine similarity, relative L1, max-abs error (benchmark_attn/benchmark_attn.py:69-81)."""
     a64, b64 = a.detach().double().flatten().cpu(), b.detach().double().flatten().cpu()

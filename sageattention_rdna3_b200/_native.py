@@ -65,6 +65,12 @@ def load_abi() -> ctypes.CDLL:
     lib.sage_mean_seq.argtypes = [sp, i, i, i, i, i, vp, vp]
     lib.sage_quant_qk_int8.restype = i
     lib.sage_quant_qk_int8.argtypes = [sp, sp, vp, sp, vp, i, i, i, i, i, i, i, f, vp, vp, vp, vp, vp]
+    lib.sage_fold_attn_partial.restype = i
+    lib.sage_fold_attn_partial.argtypes = [sp, vp, i64, i64, sp, i, vp, i, i, i, i, i, vp]
+    lib.sage_prep_smooth_preferred.restype = i
+    lib.sage_prep_smooth_preferred.argtypes = [i, i]
+    lib.sage_prep_smooth_qkv.restype = i
+    lib.sage_prep_smooth_qkv.argtypes = [sp, sp, sp, vp, i, i, i, i, i, i, i, f, vp, vp, vp, vp, vp, vp]
     lib.sage_quant_qk_int8_smooth_static.restype = i
     lib.sage_quant_qk_int8_smooth_static.argtypes = [sp, sp, i, i, i, i, i, i, i, f, vp, vp, vp, vp, vp]
     lib.sage_v_to_f16.restype = i

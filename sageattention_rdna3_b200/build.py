@@ -64,7 +64,8 @@ def _run(cmd) -> None:
 
 
 def build_abi(force: bool = False, verbose: bool = False) -> Path:
-    sources = [CSRC / "sage_abi.cu", CSRC / "attn_kernel.cuh", CSRC / "prep_kernels.cuh", CSRC / "ptx_sm100.cuh",
+    sources = [CSRC / "sage_abi.cu", CSRC / "attn_kernel.cuh", CSRC / "prep_kernels.cuh", CSRC / "merge_kernels.cuh",
+               CSRC / "ptx_sm100.cuh",
                REPO_DIR / "include" / "sage_b200.h"]
     if force or not _up_to_date(LIB_ABI, sources):
         cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB_ABI), str(CSRC / "sage_abi.cu")]

@@ -38,6 +38,10 @@ struct PrepParams {
   int q_groups, k_groups;   // ceil(Sq/32), ceil(Skv/16)
   float sm_scale_log2e;
   int q_blocks, k_blocks;   // CTAs spent on Q groups, on K groups; the rest convert V
+  // sage_prep_smooth_kernel only: the mean it computes goes to k_mean_out ([B,Hkv,D], input dtype);
+  // k_clusters clusters of 8 CTAs share the (batch, kv-head) pairs between them
+  void* k_mean_out;
+  int k_clusters;
 };
 
 constexpr int kPrepThreads = 256;
@@ -90,6 +94,25 @@ template <> __device__ __forceinline__ float magnitude_to_float<__half>(uint32_t
   return __half2float(__ushort_as_half(static_cast<unsigned short>(m16)));
 }
 
+// 16-byte read-only loads with an L2 eviction priority: `evict_last` keeps lines that will be read
+// again soon ahead of streaming traffic, `evict_first` gives them up.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint4 ldg_l2_hint(const uint4* ptr, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr), "l"(policy));
+  return v;
+}
+
 template <typename T, int D, bool HAS_MEAN>
 struct RowSlab {
   static constexpr int kLanesPerRow = D / 8;
@@ -99,8 +122,12 @@ struct RowSlab {
   f32x2_t neg_mean2[4];     // -mean of my 8 columns, as pairs: x - mean == x + (-mean) exactly
   int sub, col;
 
+  // `mean_bh` (global memory, read through the read-only path) or `mean_vec` (the 8 means of this
+  // lane's columns, already in registers) - at most one of them
+  // `l2_policy` != 0: the rows are read with that L2 eviction policy.
   __device__ __forceinline__ void load(const T* __restrict__ in_bh, long long stride_s, int row0, int S,
-                                       const T* __restrict__ mean_bh, int lane) {
+                                       const T* __restrict__ mean_bh, int lane, const uint4* mean_vec = nullptr,
+                                       uint64_t l2_policy = 0) {
     sub = lane / kLanesPerRow;
     col = (lane % kLanesPerRow) * 8;
     const T* src = in_bh + static_cast<long long>(row0 + sub) * stride_s + col;
@@ -108,11 +135,14 @@ struct RowSlab {
 #pragma unroll
     for (int p = 0; p < kPasses; ++p) {
       raw[p] = make_uint4(0u, 0u, 0u, 0u);
-      if (row0 + p * kRowsPerPass + sub < S) raw[p] = __ldg(reinterpret_cast<const uint4*>(src));
+      if (row0 + p * kRowsPerPass + sub < S) {
+        raw[p] = l2_policy ? ldg_l2_hint(reinterpret_cast<const uint4*>(src), l2_policy)
+                           : __ldg(reinterpret_cast<const uint4*>(src));
+      }
       src += step;
     }
     if (HAS_MEAN) {
-      const uint4 mraw = __ldg(reinterpret_cast<const uint4*>(mean_bh + col));
+      const uint4 mraw = mean_vec ? *mean_vec : __ldg(reinterpret_cast<const uint4*>(mean_bh + col));
       const uint32_t* mw = reinterpret_cast<const uint32_t*>(&mraw);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -184,70 +214,68 @@ struct RowSlab {
   }
 };
 
-template <typename T, int D>
-__global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepParams p) {
-  __shared__ float warp_max[kPrepWarps];
+// The three kinds of block, for a block of THREADS threads.
+// Q: a group of 32 rows per warp pair.
+template <typename T, int D, int THREADS>
+__device__ __forceinline__ void prep_q_block(const PrepParams& p, int blk, float* warp_max) {
+  constexpr int kGroupsPerBlock = THREADS / 64;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  int blk = blockIdx.x;
+  const long long g = static_cast<long long>(blk) * kGroupsPerBlock + (warp >> 1);
+  const long long total = static_cast<long long>(p.B) * p.Hq * p.q_groups;
+  const bool valid = g < total;
+  const int grp = valid ? static_cast<int>(g % p.q_groups) : 0;
+  const int bh = valid ? static_cast<int>(g / p.q_groups) : 0;
+  const int b = bh / p.Hq, h = bh % p.Hq;
+  const int row0 = grp * kQGroupRows + (warp & 1) * kRowsPerWarp;
+  const int S = valid ? p.Sq : 0;
+  const T* in_bh = reinterpret_cast<const T*>(p.q.ptr) + b * p.q.stride_b + h * p.q.stride_h;
+  RowSlab<T, D, false> slab;
+  slab.load(in_bh, p.q.stride_s, row0, S, nullptr, lane);
+  const float mine = slab.abs_max(row0, S);
+  if (lane == 0) warp_max[warp] = mine;
+  __syncthreads();
+  const float vmax = fmaxf(warp_max[warp], warp_max[warp ^ 1]);
+  const float s_mul = p.sm_scale_log2e;
+  const float amax = fmaxf(1e-7f, __fmul_rn(vmax, fabsf(s_mul)));      // :192,224
+  if (valid && lane == 0 && (warp & 1) == 0) p.q_scale[g] = __fdiv_rn(amax, 127.0f);   // :244-245
+  const float iscale = __fmul_rn(__fdiv_rn(127.0f, amax), s_mul);      // :252,296
+  slab.quantise(row0, S, iscale, p.q_i8 + static_cast<long long>(bh) * p.Sq * D);
+}
 
-  if (blk < p.q_blocks) {                                   // ---- Q: a group of 32 rows per warp pair
-    const long long g = static_cast<long long>(blk) * kQGroupsPerBlock + (warp >> 1);
-    const long long total = static_cast<long long>(p.B) * p.Hq * p.q_groups;
-    const bool valid = g < total;
-    const int grp = valid ? static_cast<int>(g % p.q_groups) : 0;
-    const int bh = valid ? static_cast<int>(g / p.q_groups) : 0;
-    const int b = bh / p.Hq, h = bh % p.Hq;
-    const int row0 = grp * kQGroupRows + (warp & 1) * kRowsPerWarp;
-    const int S = valid ? p.Sq : 0;
-    const T* in_bh = reinterpret_cast<const T*>(p.q.ptr) + b * p.q.stride_b + h * p.q.stride_h;
-    RowSlab<T, D, false> slab;
-    slab.load(in_bh, p.q.stride_s, row0, S, nullptr, lane);
-    const float mine = slab.abs_max(row0, S);
-    if (lane == 0) warp_max[warp] = mine;
-    __syncthreads();
-    const float vmax = fmaxf(warp_max[warp], warp_max[warp ^ 1]);
-    const float s_mul = p.sm_scale_log2e;
-    const float amax = fmaxf(1e-7f, __fmul_rn(vmax, fabsf(s_mul)));      // :192,224
-    if (valid && lane == 0 && (warp & 1) == 0) p.q_scale[g] = __fdiv_rn(amax, 127.0f);   // :244-245
-    const float iscale = __fmul_rn(__fdiv_rn(127.0f, amax), s_mul);      // :252,296
-    slab.quantise(row0, S, iscale, p.q_i8 + static_cast<long long>(bh) * p.Sq * D);
-    return;
-  }
-  blk -= p.q_blocks;
-  if (blk < p.k_blocks) {                                   // ---- K: a group of 16 rows per warp
-    const long long g = static_cast<long long>(blk) * kKGroupsPerBlock + warp;
-    const long long total = static_cast<long long>(p.B) * p.Hkv * p.k_groups;
-    if (g >= total) return;
-    const int grp = static_cast<int>(g % p.k_groups);
-    const int bh = static_cast<int>(g / p.k_groups);
-    const int b = bh / p.Hkv, h = bh % p.Hkv;
-    const int row0 = grp * kKGroupRows;
-    const T* in_bh = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h;
-    const T* mean_bh =
-        p.k_mean ? reinterpret_cast<const T*>(p.k_mean) + static_cast<long long>(bh) * D : nullptr;
-    float* scale_out = p.k_scale + g;
-    int8_t* out_bh = p.k_i8 + static_cast<long long>(bh) * p.Skv * D;
-    auto run = [&](auto slab) {
-      slab.load(in_bh, p.k.stride_s, row0, p.Skv, mean_bh, lane);
-      const float amax = fmaxf(1e-7f, slab.abs_max(row0, p.Skv));        // s = 1 for K
-      if (lane == 0) *scale_out = __fdiv_rn(amax, 127.0f);
-      slab.quantise(row0, p.Skv, __fdiv_rn(127.0f, amax), out_bh);
-    };
-    if (mean_bh != nullptr) run(RowSlab<T, D, true>{});
-    else run(RowSlab<T, D, false>{});
-    return;
-  }
-  blk -= p.k_blocks;
-  // ---- V: 16-bit copy to fp16 [B,Hkv,Skv,D] (csrc/attn_gfx11.cu:377-381: __float2half_rn).
-  // Each thread converts four 16-byte vectors, 4096 bytes apart in the output, so a warp moves 512 B
-  // per load; the four loads are issued before the first store.  (batch*head, position) of the
-  // first vector comes from one division, the others follow by stepping 256 / (D/8) rows.
+// K: one group of 16 rows of (batch*head) `bh`, by one warp.  The mean comes from global memory
+// (`p.k_mean`) or, if `mean_vec` is given, from registers.
+template <typename T, int D>
+__device__ __forceinline__ void prep_k_group(const PrepParams& p, int bh, int grp, int lane, const uint4* mean_vec,
+                                             uint64_t l2_policy = 0) {
+  const int b = bh / p.Hkv, h = bh % p.Hkv;
+  const int row0 = grp * kKGroupRows;
+  const T* in_bh = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h;
+  const T* mean_bh =
+      (p.k_mean && !mean_vec) ? reinterpret_cast<const T*>(p.k_mean) + static_cast<long long>(bh) * D : nullptr;
+  float* scale_out = p.k_scale + static_cast<long long>(bh) * p.k_groups + grp;
+  int8_t* out_bh = p.k_i8 + static_cast<long long>(bh) * p.Skv * D;
+  auto run = [&](auto slab) {
+    slab.load(in_bh, p.k.stride_s, row0, p.Skv, mean_bh, lane, mean_vec, l2_policy);
+    const float amax = fmaxf(1e-7f, slab.abs_max(row0, p.Skv));        // s = 1 for K
+    if (lane == 0) *scale_out = __fdiv_rn(amax, 127.0f);
+    slab.quantise(row0, p.Skv, __fdiv_rn(127.0f, amax), out_bh);
+  };
+  if (mean_bh != nullptr || mean_vec != nullptr) run(RowSlab<T, D, true>{});
+  else run(RowSlab<T, D, false>{});
+}
+
+// V: 16-bit copy to fp16 [B,Hkv,Skv,D] (csrc/attn_gfx11.cu:377-381: __float2half_rn).
+// Each thread converts four 16-byte vectors, THREADS * 16 bytes apart in the output, so a warp moves
+// 512 B per load; the four loads are issued before the first store.  (batch*head, position) of the
+// first vector comes from one division, the others follow by stepping THREADS / (D/8) rows.
+template <typename T, int D, int THREADS>
+__device__ __forceinline__ void prep_v_block(const PrepParams& p, int blk) {
   if (p.v16 == nullptr) return;
   constexpr int kVecPerRow = D / 8;
-  constexpr int kRowStep = kPrepThreads / kVecPerRow;
+  constexpr int kRowStep = THREADS / kVecPerRow;
   const long long n_vec = static_cast<long long>(p.B) * p.Hkv * p.Skv * kVecPerRow;
-  const long long base = static_cast<long long>(blk) * (kPrepThreads * 4) + threadIdx.x;
+  const long long base = static_cast<long long>(blk) * (THREADS * 4) + threadIdx.x;
   const int c = static_cast<int>(base % kVecPerRow) * 8;
   const long long row0 = base / kVecPerRow;
   int bh = static_cast<int>(row0 / p.Skv);
@@ -256,7 +284,7 @@ __global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepPa
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     raw[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (base + static_cast<long long>(i) * kPrepThreads < n_vec) {
+    if (base + static_cast<long long>(i) * THREADS < n_vec) {
       const int b = bh / p.Hkv, h = bh - b * p.Hkv;
       const T* src = reinterpret_cast<const T*>(p.v.ptr) + b * p.v.stride_b + h * p.v.stride_h +
                      static_cast<long long>(s) * p.v.stride_s + c;
@@ -270,7 +298,7 @@ __global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepPa
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const long long vec = base + static_cast<long long>(i) * kPrepThreads;
+    const long long vec = base + static_cast<long long>(i) * THREADS;
     if (vec < n_vec) {
       const T* xv = reinterpret_cast<const T*>(&raw[i]);
       uint4 out;
@@ -283,6 +311,26 @@ __global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepPa
       *reinterpret_cast<uint4*>(p.v16 + vec * 8) = out;
     }
   }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPrepThreads, 4) sage_prep_kernel(const PrepParams p) {
+  __shared__ float warp_max[kPrepWarps];
+  int blk = blockIdx.x;
+  if (blk < p.q_blocks) {
+    prep_q_block<T, D, kPrepThreads>(p, blk, warp_max);
+    return;
+  }
+  blk -= p.q_blocks;
+  if (blk < p.k_blocks) {                                   // ---- K: a group of 16 rows per warp
+    const long long g = static_cast<long long>(blk) * kKGroupsPerBlock + (threadIdx.x >> 5);
+    const long long total = static_cast<long long>(p.B) * p.Hkv * p.k_groups;
+    if (g >= total) return;
+    prep_k_group<T, D>(p, static_cast<int>(g / p.k_groups), static_cast<int>(g % p.k_groups), threadIdx.x & 31, nullptr);
+    return;
+  }
+  blk -= p.k_blocks;
+  prep_v_block<T, D, kPrepThreads>(p, blk);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -391,6 +439,132 @@ __global__ void __cluster_dims__(kMeanCluster, 1, 1) __launch_bounds__(256) sage
       *out = __float2half_rn(value);
     } else {
       *out = __float2bfloat16_rn(value);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// smooth_k in one launch: K mean, quantisation of K against it, quantisation of Q and the fp16 copy of
+// V.  K is read from DRAM once: the cluster that has just summed a (batch, kv-head) quantises the same
+// rows again while they are still in L2 (2 MiB per head at S = 8192, D = 128), instead of a second
+// kernel reading all of K again after all of it has been through the cache.
+//
+// Blocks of 512 threads in clusters of 8.  The first 8 * k_clusters CTAs work on K: cluster c takes the
+// heads c, c + k_clusters, ... one after the other.  Per head:
+//   1. mean, exactly as sage_kmean_kernel: CTA r owns the partials [32r, 32r+32) of the reference's
+//      order and reads the rows that feed them; partials go to the CTA that owns their columns
+//      (distributed shared memory), which adds them serially, divides, rounds once;
+//   2. every CTA sends the D/8 means it owns to all eight CTAs (and to global memory: the caller gets
+//      the mean as well);
+//   3. each warp quantises 16-row groups of the rows its CTA read in step 1.
+// The other CTAs quantise Q and convert V as in sage_prep_kernel; they run next to the K clusters, so
+// the launch as a whole moves |Q| + |K| + |V| in and the int8 / fp16 copies out.
+constexpr int kFusedThreads = 512;
+
+__device__ __forceinline__ void st_cluster_u16(uint32_t addr, unsigned short v) {
+  asm volatile("st.shared::cluster.u16 [%0], %1;" :: "r"(addr), "h"(v) : "memory");
+}
+
+template <typename T, int D>
+__global__ void __cluster_dims__(kMeanCluster, 1, 1) __launch_bounds__(kFusedThreads, 2)
+sage_prep_smooth_kernel(const PrepParams p) {
+  constexpr int kLanesPerRow = D / 8;
+  constexpr int kActive = kMeanPartialsPerCta * kLanesPerRow;     // threads that read rows in step 1
+  constexpr int kOwnCols = D / kMeanCluster;
+  static_assert(kActive <= kFusedThreads && kOwnCols % 8 == 0, "tile shape");
+  __shared__ __align__(16) float part[kMeanPartials][kOwnCols];
+  __shared__ __align__(16) T mean_s[D];
+  __shared__ float warp_max[kFusedThreads / 32];
+
+  const int tid = threadIdx.x;
+  const int n_k_ctas = p.k_clusters * kMeanCluster;
+  if (static_cast<int>(blockIdx.x) >= n_k_ctas) {
+    int blk = blockIdx.x - n_k_ctas;
+    if (blk < p.q_blocks) {
+      prep_q_block<T, D, kFusedThreads>(p, blk, warp_max);
+      return;
+    }
+    prep_v_block<T, D, kFusedThreads>(p, blk - p.q_blocks);        // blocks past the end do nothing
+    return;
+  }
+
+  const uint32_t rank = blockIdx.x % kMeanCluster;
+  const int cluster_id = blockIdx.x / kMeanCluster;
+  const int n_heads = p.B * p.Hkv;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int rr = tid / kLanesPerRow, c = tid % kLanesPerRow;
+  const int p0 = static_cast<int>(rank) * kMeanPartialsPerCta + rr;          // the partial this thread sums
+  const int n_blocks256 = (p.Skv + kMeanPartials - 1) / kMeanPartials;
+  // K is read twice by the same CTA, a few microseconds apart, while Q and V stream through the same
+  // L2: the first read asks the L2 to keep the lines, the second gives them up.
+  const uint64_t keep = l2_policy_evict_last(), release = l2_policy_evict_first();
+
+#pragma unroll 1
+  for (int bh = cluster_id; bh < n_heads; bh += p.k_clusters) {
+    const int b = bh / p.Hkv, h = bh % p.Hkv;
+    const T* base = reinterpret_cast<const T*>(p.k.ptr) + b * p.k.stride_b + h * p.k.stride_h + c * 8;
+    cluster_arrive();       // every CTA of the cluster is here: `part` and `mean_s` of the last head are free
+
+    // ---- step 1: partial sums (csrc/attn_gfx11.cu:121-127), eight blocks of 256 rows in flight
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+    if (tid < kActive) {
+      constexpr int kUnroll = 8;
+      for (int s0 = 0; s0 < p.Skv; s0 += kMeanPartials * kUnroll) {
+        uint4 r[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int srow = s0 + u * kMeanPartials + p0;
+          r[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (srow < p.Skv) {
+            r[u] = ldg_l2_hint(reinterpret_cast<const uint4*>(base + static_cast<long long>(srow) * p.k.stride_s), keep);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int srow = s0 + u * kMeanPartials + p0;
+          if (srow < p.Skv) {                               // a missing row adds nothing (not +0.0)
+            const T* x = reinterpret_cast<const T*>(&r[u]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = __fadd_rn(acc[e], elem_to_float<T>(x[e]));
+          }
+        }
+      }
+    }
+    cluster_wait();
+    if (tid < kActive) {
+      const uint32_t owner = static_cast<uint32_t>((c * 8) / kOwnCols);
+      const uint32_t dst = map_to_cta(&part[p0][(c * 8) % kOwnCols], owner);
+      st_cluster_f32x4(dst, acc[0], acc[1], acc[2], acc[3]);
+      st_cluster_f32x4(dst + 16, acc[4], acc[5], acc[6], acc[7]);
+    }
+    cluster_arrive();
+    cluster_wait();         // all 256 partials of this CTA's columns have landed
+
+    // ---- step 2: serial sum of the partials (:131-136), one division, one rounding; to everybody
+    if (tid < kOwnCols) {
+      float sum = 0.0f;
+#pragma unroll 16
+      for (int i = 0; i < kMeanPartials; ++i) sum = __fadd_rn(sum, part[i][tid]);
+      const float value = __fdiv_rn(sum, static_cast<float>(p.Skv));
+      T m;
+      if constexpr (std::is_same<T, __half>::value) m = __float2half_rn(value);
+      else m = __float2bfloat16_rn(value);
+      const int col = static_cast<int>(rank) * kOwnCols + tid;
+      reinterpret_cast<T*>(p.k_mean_out)[static_cast<long long>(bh) * D + col] = m;
+      const unsigned short bits = *reinterpret_cast<const unsigned short*>(&m);
+#pragma unroll
+      for (uint32_t dst_rank = 0; dst_rank < kMeanCluster; ++dst_rank) st_cluster_u16(map_to_cta(&mean_s[col], dst_rank), bits);
+    }
+    cluster_arrive();
+    cluster_wait();         // the D means are in every CTA's mean_s
+
+    // ---- step 3: quantise the rows this CTA read (two 16-row groups per block of 256 rows)
+    const uint4 mean_vec = *reinterpret_cast<const uint4*>(&mean_s[(lane % kLanesPerRow) * 8]);
+    for (int u = warp; u < 2 * n_blocks256; u += kFusedThreads / 32) {
+      const int row0 = (u >> 1) * kMeanPartials + static_cast<int>(rank) * kMeanPartialsPerCta + (u & 1) * kKGroupRows;
+      if (row0 < p.Skv) prep_k_group<T, D>(p, bh, row0 / kKGroupRows, lane, &mean_vec, release);
     }
   }
 }

@@ -14,6 +14,7 @@
 #include <mutex>
 
 #include "attn_kernel.cuh"
+#include "merge_kernels.cuh"
 #include "prep_kernels.cuh"
 
 // K-mean scratch of sage_quant_qk_int8_smooth_static: part of the library image, never allocated.
@@ -424,6 +425,79 @@ int sage_quant_qk_int8(const sage_strided_t* q, const sage_strided_t* k, const v
   return dispatch_prep(dtype, D, p, v_blocks, static_cast<cudaStream_t>(stream));
 }
 
+int sage_prep_smooth_preferred(int B, int Hkv) {
+  // The one-launch form keeps one cluster of 8 CTAs busy per (batch, kv-head) for the length of a
+  // dependent chain (sum, exchange, quantise: about 30 us at S = 8192): it wins while all heads are
+  // resident at once with room to spare for the Q and V blocks, i.e. up to a quarter of the CTA slots.
+  int sms = 0;
+  if (B <= 0 || Hkv <= 0 || sm_count(&sms) != SAGE_OK) return 0;
+  return static_cast<long long>(B) * Hkv <= sms / sage::kMeanCluster ? 1 : 0;
+}
+
+int sage_prep_smooth_qkv(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v, void* v16, int dtype,
+                         int B, int Hq, int Hkv, int Sq, int Skv, int D, float sm_scale, int8_t* q_i8, float* q_scale,
+                         int8_t* k_i8, float* k_scale, void* k_mean_out, void* stream) {
+  SAGE_REQUIRE(Sq <= 0 || (q && q->ptr && q_i8 && q_scale), "sage_prep_smooth_qkv: null q pointer");
+  SAGE_REQUIRE(k && k->ptr && k_i8 && k_scale && k_mean_out, "sage_prep_smooth_qkv: null k pointer");
+  SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_prep_smooth_qkv: dtype must be f16 or bf16");
+  SAGE_REQUIRE(D == 64 || D == 128, "sage_prep_smooth_qkv: head_dim must be 64 or 128, got %d", D);
+  SAGE_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Sq >= 0 && Skv >= 1, "sage_prep_smooth_qkv: bad sizes (Skv must be >= 1)");
+  SAGE_REQUIRE(Sq <= 0 || (aligned16(q->ptr) && strides_ok(q) && aligned16(q_i8)),
+               "sage_prep_smooth_qkv: q needs a 16-byte aligned base and strides % 8 == 0, q_i8 a 16-byte aligned base");
+  SAGE_REQUIRE(aligned16(k->ptr) && strides_ok(k) && aligned16(k_i8) && aligned16(k_mean_out),
+               "sage_prep_smooth_qkv: k needs a 16-byte aligned base and strides % 8 == 0, k_i8 / k_mean 16-byte aligned bases");
+  const bool do_v = (v != nullptr && v16 != nullptr);
+  if (do_v) {
+    SAGE_REQUIRE(v->ptr && aligned16(v->ptr) && strides_ok(v) && aligned16(v16),
+                 "sage_prep_smooth_qkv: v / v16 need 16-byte aligned bases and strides % 8 == 0");
+  }
+  sage::PrepParams p;
+  memset(&p, 0, sizeof(p));
+  if (Sq > 0) p.q = view_of(q);
+  p.k = view_of(k);
+  if (do_v) p.v = view_of(v);
+  p.q_i8 = q_i8; p.k_i8 = k_i8; p.q_scale = q_scale; p.k_scale = k_scale;
+  p.v16 = do_v ? static_cast<__half*>(v16) : nullptr;
+  p.k_mean_out = k_mean_out;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv;
+  p.q_groups = (Sq + sage::kQGroupRows - 1) / sage::kQGroupRows;
+  p.k_groups = (Skv + sage::kKGroupRows - 1) / sage::kKGroupRows;
+  volatile float s = sm_scale;                          // csrc/attn_gfx11.cu:34,1995: one fp32 multiply
+  volatile float l2e = 1.4426950408889634f;
+  p.sm_scale_log2e = s * l2e;
+  // K clusters: at most two K CTAs per SM at a time, every cluster the same number of heads (+-1)
+  int sms = 0;
+  int rc = sm_count(&sms);
+  if (rc) return rc;
+  const int n_heads = B * Hkv;
+  const int max_clusters = std::max(1, 2 * sms / sage::kMeanCluster);
+  const int rounds = (n_heads + max_clusters - 1) / max_clusters;
+  p.k_clusters = (n_heads + rounds - 1) / rounds;
+  constexpr int kQGroupsPerBlock = sage::kFusedThreads / 64;
+  const long long qg = static_cast<long long>(B) * Hq * p.q_groups;
+  p.q_blocks = static_cast<int>((qg + kQGroupsPerBlock - 1) / kQGroupsPerBlock);
+  p.k_blocks = p.k_clusters * sage::kMeanCluster;
+  long long v_blocks = 0;
+  if (do_v) {
+    const long long n_vec = static_cast<long long>(B) * Hkv * Skv * (D / 8);
+    v_blocks = (n_vec + sage::kFusedThreads * 4 - 1) / (sage::kFusedThreads * 4);
+  }
+  long long grid = p.k_blocks + p.q_blocks + v_blocks;
+  grid = (grid + sage::kMeanCluster - 1) / sage::kMeanCluster * sage::kMeanCluster;     // whole clusters
+  SAGE_REQUIRE(grid <= 0x7fffffffLL, "sage_prep_smooth_qkv: too many blocks for one launch (%lld)", grid);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned g = static_cast<unsigned>(grid);
+  if (dtype == SAGE_DTYPE_F16) {
+    if (D == 128) sage::sage_prep_smooth_kernel<__half, 128><<<g, sage::kFusedThreads, 0, st>>>(p);
+    else sage::sage_prep_smooth_kernel<__half, 64><<<g, sage::kFusedThreads, 0, st>>>(p);
+  } else {
+    if (D == 128) sage::sage_prep_smooth_kernel<__nv_bfloat16, 128><<<g, sage::kFusedThreads, 0, st>>>(p);
+    else sage::sage_prep_smooth_kernel<__nv_bfloat16, 64><<<g, sage::kFusedThreads, 0, st>>>(p);
+  }
+  SAGE_CUDA(cudaGetLastError());
+  return SAGE_OK;
+}
+
 int sage_quant_qk_int8_smooth_static(const sage_strided_t* q, const sage_strided_t* k, int dtype, int B, int Hq,
                                      int Hkv, int Sq, int Skv, int D, float sm_scale, int8_t* q_i8, float* q_scale,
                                      int8_t* k_i8, float* k_scale, void* stream) {
@@ -558,6 +632,37 @@ int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sa
   if (D == 128) return is_causal ? SAGE_LAUNCH(128, true) : SAGE_LAUNCH(128, false);
   return is_causal ? SAGE_LAUNCH(64, true) : SAGE_LAUNCH(64, false);
 #undef SAGE_LAUNCH
+}
+
+int sage_fold_attn_partial(const sage_strided_t* o_acc, float* lse_acc, int64_t lse_stride_b, int64_t lse_stride_h,
+                           const sage_strided_t* o_part, int part_dtype, const float* lse_part, int B, int H, int S, int D,
+                           int first, void* stream) {
+  SAGE_REQUIRE(o_acc && o_acc->ptr && lse_acc && o_part && o_part->ptr && lse_part, "sage_fold_attn_partial: null pointer");
+  SAGE_REQUIRE(part_dtype == SAGE_DTYPE_F16 || part_dtype == SAGE_DTYPE_BF16, "sage_fold_attn_partial: the partial must be f16 or bf16");
+  SAGE_REQUIRE(D == 64 || D == 128, "sage_fold_attn_partial: head_dim must be 64 or 128, got %d", D);
+  SAGE_REQUIRE(B >= 0 && H >= 0 && S >= 0, "sage_fold_attn_partial: bad sizes");
+  SAGE_REQUIRE((reinterpret_cast<uintptr_t>(o_acc->ptr) & 31u) == 0 && o_acc->stride_b % 8 == 0 && o_acc->stride_h % 8 == 0 &&
+                   o_acc->stride_s % 8 == 0,
+               "sage_fold_attn_partial: the fp32 accumulator needs a 32-byte aligned base and strides % 8 == 0");
+  SAGE_REQUIRE(aligned16(o_part->ptr) && strides_ok(o_part),
+               "sage_fold_attn_partial: the partial needs a 16-byte aligned base and strides % 8 == 0");
+  const long long n_vec = static_cast<long long>(B) * H * S * (D / 8);
+  if (n_vec == 0) return SAGE_OK;
+  sage::FoldParams p;
+  p.o_acc = const_cast<float*>(static_cast<const float*>(o_acc->ptr));
+  p.acc_stride_b = o_acc->stride_b; p.acc_stride_h = o_acc->stride_h; p.acc_stride_s = o_acc->stride_s;
+  p.lse_acc = lse_acc; p.lse_acc_stride_b = lse_stride_b; p.lse_acc_stride_h = lse_stride_h;
+  p.o_part = o_part->ptr;
+  p.part_stride_b = o_part->stride_b; p.part_stride_h = o_part->stride_h; p.part_stride_s = o_part->stride_s;
+  p.lse_part = lse_part;
+  p.B = B; p.H = H; p.S = S; p.D = D;
+  p.part_bf16 = (part_dtype == SAGE_DTYPE_BF16);
+  p.first = first ? 1 : 0;
+  const long long blocks = (n_vec + sage::kFoldThreads - 1) / sage::kFoldThreads;
+  SAGE_REQUIRE(blocks <= 0x7fffffffLL, "sage_fold_attn_partial: too many blocks for one launch (%lld)", blocks);
+  sage::sage_fold_partial_kernel<<<static_cast<unsigned>(blocks), sage::kFoldThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  SAGE_CUDA(cudaGetLastError());
+  return SAGE_OK;
 }
 
 int sage_direct_attn(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,

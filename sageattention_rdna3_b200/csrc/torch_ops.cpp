@@ -136,6 +136,49 @@ std::vector<at::Tensor> prep_qkv(const at::Tensor& q, const at::Tensor& k, const
   return quant_impl(q, k, k_mean, &v, layout, sm_scale);
 }
 
+// prep_smooth_qkv(Tensor query, Tensor key, Tensor? value, int tensor_layout, float sm_scale) -> Tensor[]
+// smooth_k in one launch: what mean_seq followed by quant_qk_int8 / prep_qkv computes (the sequence of
+// sageattention/core.py:186-193), with K read from DRAM once.  Returns [q_int8, q_scale, k_int8,
+// k_scale, key_mean] and, if `value` is given, its fp16 copy [B,Hkv,Skv,D] as a sixth tensor.
+std::vector<at::Tensor> prep_smooth_qkv(const at::Tensor& q, const at::Tensor& k, const c10::optional<at::Tensor>& v,
+                                        int64_t layout, double sm_scale) {
+  check_16b(q, "query");
+  check_16b(k, "key");
+  TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.device() == k.device(), "query/key dtype or device mismatch");
+  const Dims dq = dims_of(q, layout), dk = dims_of(k, layout);
+  TORCH_CHECK(dq.B == dk.B && dq.D == dk.D, "query/key batch or head_dim mismatch");
+  TORCH_CHECK(dq.D == 64 || dq.D == 128, "head_dim must be 64 or 128, got ", dq.D);
+  TORCH_CHECK(dk.S >= 1 && dk.B >= 1 && dk.H >= 1 && dq.H >= 1, "prep_smooth_qkv needs at least one key");
+  c10::cuda::CUDAGuard guard(q.device());
+  const auto i8 = q.options().dtype(at::kChar);
+  const auto f32 = q.options().dtype(at::kFloat);
+  at::Tensor q_i8 = at::empty({dq.B, dq.H, dq.S, dq.D}, i8);
+  at::Tensor k_i8 = at::empty({dk.B, dk.H, dk.S, dk.D}, i8);
+  at::Tensor q_scale = at::empty({dq.B, dq.H, (dq.S + 31) / 32}, f32);
+  at::Tensor k_scale = at::empty({dk.B, dk.H, (dk.S + 15) / 16}, f32);
+  at::Tensor k_mean = at::empty({dk.B, dk.H, dk.D}, k.options());
+  const sage_strided_t qs = strided_of(q, layout), ks = strided_of(k, layout);
+  sage_strided_t vs;
+  at::Tensor v16;
+  const bool convert_v = v.has_value();
+  if (convert_v) {
+    check_16b(*v, "value");
+    const Dims dv = dims_of(*v, layout);
+    TORCH_CHECK(dv.B == dk.B && dv.H == dk.H && dv.S == dk.S && dv.D == dk.D, "key/value shape mismatch");
+    TORCH_CHECK(v->scalar_type() == k.scalar_type(), "key/value dtype mismatch");
+    v16 = at::empty({dk.B, dk.H, dk.S, dk.D}, q.options().dtype(at::kHalf));
+    vs = strided_of(*v, layout);
+  }
+  check_rc(sage_prep_smooth_qkv(&qs, &ks, convert_v ? &vs : nullptr, convert_v ? v16.data_ptr() : nullptr, dtype_code(q),
+                                (int)dq.B, (int)dq.H, (int)dk.H, (int)dq.S, (int)dk.S, (int)dq.D,
+                                static_cast<float>(sm_scale), q_i8.data_ptr<int8_t>(), q_scale.data_ptr<float>(),
+                                k_i8.data_ptr<int8_t>(), k_scale.data_ptr<float>(), k_mean.data_ptr(), current_stream(q)),
+           "prep_smooth_qkv");
+  std::vector<at::Tensor> out{q_i8, q_scale, k_i8, k_scale, k_mean};
+  if (convert_v) out.push_back(v16);
+  return out;
+}
+
 // v_to_f16(Tensor value, int tensor_layout) -> Tensor: the dtype half of the reference's
 // v_transpose (csrc/pybind_gfx11.cpp:37); output is [B,H,S,D] contiguous fp16.
 at::Tensor v_to_f16(const at::Tensor& v, int64_t layout) {
@@ -319,6 +362,16 @@ std::vector<at::Tensor> sageattn_fwd_impl(const at::Tensor& q, const at::Tensor&
     }
     return {o};
   }
+  const Dims dk_all = dims_of(k, layout);
+  c10::cuda::CUDAGuard guard(q.device());
+  if (smooth_k && sage_prep_smooth_preferred((int)dk_all.B, (int)dk_all.H)) {
+    // few heads: one launch for the mean and the quantisation against it
+    std::vector<at::Tensor> parts =
+        prep_smooth_qkv(q, k, bf16 ? c10::optional<at::Tensor>(v) : c10::optional<at::Tensor>(), layout, sm_scale);
+    qk_int8_sv_f16_attn(parts[0], parts[2], bf16 ? parts[5] : v, o, parts[1], parts[3], layout, is_causal, sm_scale,
+                        bf16 ? kHND : layout, none, st, lse);
+    return {o, parts[4]};
+  }
   at::Tensor k_mean = smooth_k ? mean_seq(k, layout) : at::empty({0}, q.options());
   std::vector<at::Tensor> parts = quant_impl(q, k, k_mean, bf16 ? &v : nullptr, layout, sm_scale);
   qk_int8_sv_f16_attn(parts[0], parts[2], bf16 ? parts[4] : v, o, parts[1], parts[3], layout, is_causal, sm_scale,
@@ -327,9 +380,34 @@ std::vector<at::Tensor> sageattn_fwd_impl(const at::Tensor& q, const at::Tensor&
   return {o};
 }
 
+// fold_partial(Tensor(a!) o_acc, Tensor(b!) lse_acc, Tensor o_part, Tensor lse_part, int tensor_layout, int first) -> ()
+// One launch that folds a partial result (o_part fp16 / bf16 in `tensor_layout`, lse_part fp32 [B,H,S])
+// into fp32 accumulators (o_acc in `tensor_layout`, lse_acc [B,H,S]; both may be row slices of larger
+// tensors).  The merge step of attention over a sequence split across GPUs.
+void fold_partial(at::Tensor& o_acc, at::Tensor& lse_acc, const at::Tensor& o_part, const at::Tensor& lse_part,
+                  int64_t layout, int64_t first) {
+  TORCH_CHECK(o_acc.is_cuda() && o_acc.scalar_type() == at::kFloat && o_acc.dim() == 4 && o_acc.stride(-1) == 1,
+              "o_acc must be a 4-D fp32 CUDA tensor with a contiguous last dim");
+  check_16b(o_part, "o_part");
+  const Dims d = dims_of(o_part, layout), da = dims_of(o_acc, layout);
+  TORCH_CHECK(da.B == d.B && da.H == d.H && da.S == d.S && da.D == d.D, "o_acc and o_part differ in shape");
+  TORCH_CHECK(lse_part.scalar_type() == at::kFloat && lse_part.is_contiguous() && lse_part.numel() == d.B * d.H * d.S,
+              "lse_part must be a contiguous fp32 [B,H,S] tensor");
+  TORCH_CHECK(lse_acc.scalar_type() == at::kFloat && lse_acc.dim() == 3 && lse_acc.size(0) == d.B && lse_acc.size(1) == d.H &&
+                  lse_acc.size(2) == d.S && lse_acc.stride(2) == 1,
+              "lse_acc must be an fp32 [B,H,S] tensor with a contiguous last dim");
+  c10::cuda::CUDAGuard guard(o_part.device());
+  const sage_strided_t acc = strided_of(o_acc, layout), part = strided_of(o_part, layout);
+  check_rc(sage_fold_attn_partial(&acc, lse_acc.data_ptr<float>(), lse_acc.stride(0), lse_acc.stride(1), &part,
+                                  dtype_code(o_part), lse_part.data_ptr<float>(), (int)d.B, (int)d.H, (int)d.S, (int)d.D,
+                                  (int)first, current_stream(o_part)),
+           "fold_partial");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(sageattention, m) {
+  m.def("fold_partial(Tensor(a!) o_acc, Tensor(b!) lse_acc, Tensor o_part, Tensor lse_part, int tensor_layout, int first) -> ()");
   m.def("sageattn_fwd(Tensor query, Tensor key, Tensor value, int tensor_layout, int is_causal, float sm_scale, "
         "int smooth_k, int use_direct, Tensor status, Tensor? lse=None, Tensor? status_host=None) -> Tensor[]");
   m.def("fp16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
@@ -342,6 +420,7 @@ TORCH_LIBRARY(sageattention, m) {
   m.def("quant_qk_int8(Tensor query, Tensor key, Tensor key_mean, int tensor_layout, float sm_scale) -> Tensor[]");
   m.def("prep_qkv(Tensor query, Tensor key, Tensor value, Tensor key_mean, int tensor_layout, float sm_scale) "
         "-> Tensor[]");
+  m.def("prep_smooth_qkv(Tensor query, Tensor key, Tensor? value, int tensor_layout, float sm_scale) -> Tensor[]");
   m.def("mean_seq(Tensor input, int tensor_layout) -> Tensor");
   m.def("v_to_f16(Tensor value, int tensor_layout) -> Tensor");
 }
@@ -353,6 +432,8 @@ TORCH_LIBRARY_IMPL(sageattention, CUDA, m) {
   m.impl("bf16_attn", &bf16_attn);
   m.impl("quant_qk_int8", &quant_qk_int8);
   m.impl("prep_qkv", &prep_qkv);
+  m.impl("fold_partial", &fold_partial);
+  m.impl("prep_smooth_qkv", &prep_smooth_qkv);
   m.impl("mean_seq", &mean_seq);
   m.impl("v_to_f16", &v_to_f16);
 }

@@ -74,6 +74,29 @@ def abi_quant(q, k, k_mean, layout, sm_scale, v=None):
     return q_i8, q_scale, k_i8, k_scale, v16
 
 
+def abi_prep_smooth(q, k, layout, sm_scale, v=None):
+    """sage_prep_smooth_qkv: (q_i8, q_scale, k_i8, k_scale, k_mean, v16 or None)."""
+    lib = _native.load_abi()
+    B, Hq, Sq, D = dims(q, layout)
+    _, Hkv, Skv, _ = dims(k, layout)
+    dev = q.device
+    q_i8 = torch.empty(B, Hq, Sq, D, dtype=torch.int8, device=dev)
+    k_i8 = torch.empty(B, Hkv, Skv, D, dtype=torch.int8, device=dev)
+    q_scale = torch.empty(B, Hq, (Sq + 31) // 32, dtype=torch.float32, device=dev)
+    k_scale = torch.empty(B, Hkv, (Skv + 15) // 16, dtype=torch.float32, device=dev)
+    k_mean = torch.empty(B, Hkv, D, dtype=k.dtype, device=dev)
+    qs, ks = strided(q, layout), strided(k, layout)
+    v16, vs_ref, v16_ptr = None, None, None
+    if v is not None:
+        v16 = torch.empty(B, Hkv, Skv, D, dtype=torch.float16, device=dev)
+        vs = strided(v, layout)
+        vs_ref, v16_ptr = ctypes.byref(vs), v16.data_ptr()
+    _check(lib.sage_prep_smooth_qkv(ctypes.byref(qs), ctypes.byref(ks), vs_ref, v16_ptr, dtype_code(q), B, Hq, Hkv, Sq,
+                                    Skv, D, float(sm_scale), q_i8.data_ptr(), q_scale.data_ptr(), k_i8.data_ptr(),
+                                    k_scale.data_ptr(), k_mean.data_ptr(), _stream()), "sage_prep_smooth_qkv")
+    return q_i8, q_scale, k_i8, k_scale, k_mean, v16
+
+
 def abi_v_to_f16(v, layout):
     lib = _native.load_abi()
     B, H, S, D = dims(v, layout)

@@ -95,6 +95,41 @@ def test_quant_and_mean_bit_exact(dev, case):
     assert bits_equal(H.abi_v_to_f16(vd, layout), so.v_to_f16(vh).contiguous())
 
 
+SMOOTH_CASES = [
+    # B, Hq, Hkv, Sq, Skv, D, dtype, layout, k_offset
+    (2, 8, 8, 8192, 8192, 128, torch.bfloat16, "HND", 2.5),      # B=2 H=32 S=8192 D=128 with fewer heads
+    (1, 40, 40, 1024, 1024, 128, torch.bfloat16, "HND", 1.0),    # more heads than clusters: several heads per cluster
+    (1, 4, 2, 1000, 3001, 64, torch.float16, "NHD", -1.5),       # head_dim 64, ragged, GQA, cross lengths
+    (2, 3, 3, 33, 65, 128, torch.float16, "NHD", 0.5),
+    (1, 2, 1, 300, 1, 64, torch.bfloat16, "HND", 3.0),           # a single key
+    (1, 1, 1, 0, 700, 128, torch.bfloat16, "HND", 0.0),          # keys only (Sq = 0)
+]
+
+
+@pytest.mark.parametrize("case", SMOOTH_CASES, ids=lambda c: "-".join(str(x).replace("torch.", "") for x in c))
+def test_one_launch_smooth_prep_is_bit_identical_to_the_two_launches(dev, case):
+    """sage_prep_smooth_qkv (mean and quantisation against it in one launch, K read once) against
+    sage_mean_seq + sage_quant_qk_int8, and against the oracle."""
+    B, Hq, Hkv, Sq, Skv, D, dtype, layout, k_off = case
+    sq, sk = shapes(B, Hq, Hkv, Sq, Skv, D, layout)
+    q, k, v = H.randn(sq, 0, dtype), H.randn(sk, 1, dtype, offset=k_off), H.randn(sk, 2, dtype)
+    sm = D ** -0.5
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    mean = H.abi_mean_seq(kd, layout)
+    want = H.abi_quant(qd, kd, mean, layout, sm, v=vd)
+    got = H.abi_prep_smooth(qd, kd, layout, sm, v=vd)
+    torch.cuda.synchronize()
+    assert bits_equal(got[4], mean), "K mean differs"
+    for name, a, b in zip(("q_i8", "q_scale", "k_i8", "k_scale"), got[:4], want[:4]):
+        assert bits_equal(a, b), f"{name} differs from the two-launch path"
+    assert bits_equal(got[5], want[4]), "fp16 copy of V differs"
+    if Skv <= 4096:
+        kh = so.to_hnd(k, layout)
+        assert bits_equal(got[4], so.mean_seq(kh)), "K mean differs from the oracle"
+        ref = so.quant_qk_int8(so.to_hnd(q, layout), kh, so.mean_seq(kh), sm)
+        assert bits_equal(got[2], ref[2]) and bits_equal(got[3], ref[3]), "K differs from the oracle"
+
+
 ATTN_CASES = [
     # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal
     (1, 1, 1, 128, 128, 128, torch.float16, "HND", False),
