@@ -498,6 +498,9 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: 'strong' shards the workload's (batch, kv-head) units over the ranks (default); "
                          "'weak' runs the whole workload on every rank (independent replicas)")
+    ap.add_argument("--units", type=int, default=0,
+                    help="N = 1 only: run this many (batch, kv-head) units of the workload instead of all of them - a "
+                         "trimmed case for profiler captures, not a benchmark result")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-gather", action="store_true")
@@ -539,6 +542,8 @@ def main():
     total_units = w["B"] * w["Hkv"]
     strong = args.scaling == "strong"
     sizes = [s.n_units for s in plan_shards(w["B"], w["Hq"], w["Hkv"], world)] if strong else [total_units] * world
+    if args.units > 0 and world == 1:
+        sizes = [min(args.units, total_units)]
     units = sizes[rank]
     prob = Problem(w, name, units, full=(units == total_units), seed_offset=100 * rank, dev=dev, ops=ops, lib=lib)
 
@@ -587,7 +592,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_public, "higher_is_better": True,
             "scaling": args.scaling if world > 1 else "strong", "vs_baseline": None, "dtype": DTYPE_NOTE,
             "data": "synthetic",
-            "config": {"workload": workload_string(name, w)},
+            "config": {"workload": workload_string(name, w) +
+                       (f" (TRIMMED to {units} of {total_units} units)" if units != total_units and world == 1 else "")},
             "per_gpu": {"units": sizes, "shape": f"B={prob.Bl} Hq={prob.Hql} Hkv={prob.Hkvl}",
                         "l2": "inputs larger than L2, no flush" if in_bytes > 126e6 else "inputs fit in L2, no flush"},
             "timed_call": "sageattn(q, k, v, kernel='int8') on HBM-resident inputs, max over ranks",
