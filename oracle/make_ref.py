@@ -25,7 +25,8 @@ from pathlib import Path
 
 ORACLE_DIR = Path(__file__).resolve().parent
 REF_OUT = ORACLE_DIR / "_ref"
-DEFAULT_REFERENCE = Path(os.environ.get("SAGE_REFERENCE_DIR", "/root/reference"))
+# where a checkout of the reference lies: SAGE_REFERENCE_DIR, else a sibling of this repository
+DEFAULT_REFERENCE = Path(os.environ.get("SAGE_REFERENCE_DIR", str(ORACLE_DIR.parent.parent / "reference")))
 FILES = {
     "sageattention/triton_backend.py": "ref_triton_backend.py",
     "test_sageattn_rdna3.py": "test_sageattn_rdna3.py",

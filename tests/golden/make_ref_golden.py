@@ -56,4 +56,4 @@ def main(outdir: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "ref_golden"))
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "_new"))

@@ -43,9 +43,9 @@ def test_plan_shards_covers_all_units_once(B, Hq, Hkv, world):
 
 
 def test_plan_shards_baseline_configs():
-    assert [s.n_units for s in plan_shards(2, 32, 32, 8)] == [8] * 8          # config 3
-    assert [s.n_units for s in plan_shards(4, 32, 8, 8)] == [4] * 8           # config 4 (4 q heads per unit)
-    assert [s.n_units for s in plan_shards(1, 24, 24, 8)] == [3] * 8          # config 5
+    assert [s.n_units for s in plan_shards(2, 32, 32, 8)] == [8] * 8          # B=2 H=32
+    assert [s.n_units for s in plan_shards(4, 32, 8, 8)] == [4] * 8           # B=4 Hq=32 Hkv=8 (4 q heads per unit)
+    assert [s.n_units for s in plan_shards(1, 24, 24, 8)] == [3] * 8          # B=1 H=24
     assert [s.n_units for s in plan_shards(1, 24, 24, 4)] == [6] * 4
     with pytest.raises(ValueError):
         plan_shards(1, 6, 4, 2)
@@ -85,7 +85,7 @@ def test_kernel_dispatch_table_of_the_reference(monkeypatch):
     assert ud(128, "HND", False, 2048, 2048) and not ud(128, "HND", True, 2049, 2049)
     assert ud(128, "HND", False, 512, 4096) and not ud(128, "HND", False, 2048, 4096)
     assert not ud(128, "NHD", False, 512, 4097)
-    # the five BASELINE configurations: 1 -> un-quantised, 2..5 -> INT8
+    # the five benchmark configurations: the smallest -> un-quantised, the others -> INT8
     assert ud(64, "HND", False, 1024, 1024)
     assert not ud(64, "NHD", False, 4096, 4096) and not ud(128, "HND", True, 8192, 8192)
     assert not ud(128, "HND", True, 4096, 4096) and not ud(128, "NHD", False, 32768, 32768)

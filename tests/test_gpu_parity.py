@@ -58,11 +58,11 @@ def outliers(x, seed, frac=0.01, gain=20.0):
 
 QUANT_CASES = [
     # B, Hq, Hkv, Sq, Skv, D, dtype, layout, smooth_k, sm_scale, k_offset, with_outliers
-    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, None, 0.0, False),      # BASELINE config 1
-    (1, 10, 10, 4096, 4096, 64, torch.float16, "NHD", False, None, 0.0, False),    # config 2 (full size)
-    (1, 2, 2, 8192, 8192, 128, torch.bfloat16, "HND", True, None, 2.5, False),     # config 3, two heads
-    (1, 4, 1, 4096, 4096, 128, torch.bfloat16, "HND", False, None, 0.0, True),     # config 4, one GQA unit
-    (1, 1, 1, 4096, 4096, 128, torch.float16, "NHD", False, None, 0.0, False),     # config 5 shape, trimmed S
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, None, 0.0, False),      # the benchmark's smallest shape
+    (1, 10, 10, 4096, 4096, 64, torch.float16, "NHD", False, None, 0.0, False),    # B=1 H=10 S=4096 D=64 NHD (full size)
+    (1, 2, 2, 8192, 8192, 128, torch.bfloat16, "HND", True, None, 2.5, False),     # S=8192 D=128 bf16 smooth_k, two heads
+    (1, 4, 1, 4096, 4096, 128, torch.bfloat16, "HND", False, None, 0.0, True),     # GQA 4:1 with outliers, one unit
+    (1, 1, 1, 4096, 4096, 128, torch.float16, "NHD", False, None, 0.0, False),     # D=128 fp16 NHD, trimmed S
     (2, 4, 2, 300, 333, 128, torch.bfloat16, "NHD", True, None, 1.5, False),
     (1, 3, 3, 33, 65, 64, torch.bfloat16, "HND", True, 0.5, -1.0, False),
     (1, 2, 2, 1, 1, 64, torch.float16, "HND", False, None, 0.0, False),
@@ -134,7 +134,7 @@ ATTN_CASES = [
     # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal
     (1, 1, 1, 128, 128, 128, torch.float16, "HND", False),
     (1, 1, 1, 128, 128, 64, torch.float16, "HND", False),
-    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False),         # BASELINE config 1
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False),         # the benchmark's smallest shape
     (1, 2, 2, 256, 384, 128, torch.float16, "HND", False),
     (1, 2, 1, 512, 512, 128, torch.bfloat16, "HND", True),
     (2, 4, 2, 300, 333, 64, torch.bfloat16, "NHD", True),
@@ -241,7 +241,7 @@ def test_gpu_matches_golden_fixtures(dev, name):
 
 
 # ----------------------------------------------------------------------------------------------
-# BASELINE sizes.  The oracle cannot do the whole of configs 3-5 in seconds, so: (a) full-size
+# Full benchmark sizes.  The oracle cannot do the whole of the three long shapes in seconds, so: (a) full-size
 # launches are checked through size-independent properties, (b) whole (batch, kv-head) units or row
 # blocks of them are compared with the oracle.
 def test_config3_full_size_properties_and_sampled_units(dev, monkeypatch):
@@ -489,7 +489,7 @@ def test_lse_through_the_c_abi_and_merge_of_two_kv_halves(dev):
 # against fp32 SDPA with the reference's own gates.
 DIRECT_CASES = [
     # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, sm_scale
-    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, None),     # BASELINE config 1: the reference runs it here
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, None),     # the reference's CPU-runnable benchmark shape: the reference runs it here
     (1, 2, 2, 1024, 1024, 128, torch.bfloat16, "HND", True, None),
     (2, 4, 2, 300, 333, 128, torch.bfloat16, "NHD", False, None),     # GQA, ragged, cross lengths
     (1, 3, 3, 33, 65, 64, torch.bfloat16, "HND", True, 0.5),
@@ -605,7 +605,7 @@ def test_one_sided_quantisation_through_the_c_abi(dev):
 # softmax; the merge adds fp32 roundings) and with the oracle.
 STREAMK_CASES = [
     # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth_k, kernel
-    (1, 10, 10, 4096, 4096, 64, torch.float16, "NHD", False, False, "int8"),    # BASELINE config 2: 320 items
+    (1, 10, 10, 4096, 4096, 64, torch.float16, "NHD", False, False, "int8"),    # the reference's headline shape: 320 items
     (2, 32, 32, 2048, 2048, 128, torch.bfloat16, "HND", True, True, "int8"),    # many short causal items per CTA
     (1, 4, 1, 1000, 1000, 128, torch.bfloat16, "HND", True, False, "int8"),     # GQA, ragged
     (1, 3, 3, 4096, 4096, 128, torch.bfloat16, "NHD", False, False, "int8"),    # few heads (VAE shapes)
@@ -650,8 +650,8 @@ def test_persistent_launch_matches_plain_launch_and_oracle(dev, monkeypatch, cas
 
 def test_scheduler_choices_for_known_shapes(dev, monkeypatch):
     """sage_attn_workspace_bytes > 0 means the persistent launch will be used.  The choices below are
-    the measured ones: 320 items of 32 steps (BASELINE config 2) and the 4-head VAE shape gain from
-    it, one exact wave, two nearly full waves and the 4096-item config 3 do not."""
+    the measured ones: 320 items of 32 steps (the reference's headline shape) and the 4-head VAE shape gain from
+    it, one exact wave, two nearly full waves and the 4096-item B=2 H=32 S=8192 causal shape do not."""
     H.set_streamk(-1)
     lib = H._native.load_abi()
     torch.cuda.set_device(dev)
@@ -662,8 +662,8 @@ def test_scheduler_choices_for_known_shapes(dev, monkeypatch):
     assert want(1, 1, 8192, 8192, 128, 1) > 0                 # one causal head: 64 very unequal items
     assert want(1, 2 * sms // 8, 1024, 4096, 128, 0) == 0     # exactly one wave of items
     assert want(1, 16, 4096, 4096, 128, 0) == 0               # 512 items: the tail wave runs alone on its SMs
-    assert want(2, 32, 8192, 8192, 128, 1) == 0               # BASELINE config 3
-    assert want(1, 24, 32768, 32768, 128, 0) == 0             # BASELINE config 5
+    assert want(2, 32, 8192, 8192, 128, 1) == 0               # B=2 H=32 S=8192 causal
+    assert want(1, 24, 32768, 32768, 128, 0) == 0             # B=1 H=24 S=32768
     assert want(1, 2, 128, 0, 64, 0) == 0 and want(1, 2, 0, 128, 64, 0) == 0
     H.set_streamk(0)
     assert want(1, 10, 4096, 4096, 64, 0) == 0

@@ -30,7 +30,7 @@ REF_CASES = [
     # B, Hq, Hkv, Sq, Skv, D, dtype, layout, causal, smooth_k, sm_scale
     (1, 2, 2, 128, 128, 64, torch.float16, "HND", False, False, None),
     (1, 2, 2, 512, 512, 128, torch.float16, "HND", False, False, None),
-    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, False, None),      # BASELINE config 1
+    (1, 2, 2, 1024, 1024, 64, torch.float16, "HND", False, False, None),      # the benchmark's smallest shape
     (2, 4, 4, 256, 256, 64, torch.float16, "NHD", False, False, None),
     (1, 4, 4, 256, 256, 128, torch.bfloat16, "HND", False, False, None),
     (1, 2, 2, 256, 256, 64, torch.float16, "HND", False, False, 0.5),
