@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SAGE_ABI_VERSION 5
+#define SAGE_ABI_VERSION 6
 
 #define SAGE_DTYPE_F16 0
 #define SAGE_DTYPE_BF16 1
@@ -51,11 +51,18 @@ const char* sage_last_error(void);
  * NULL such a failure goes unreported and the output is left partly unwritten.  The reference has
  * no counterpart (its launchers check nothing after the launch, csrc/attn_gfx11.cu:2069-2273).
  *
+ * sage_set_status_mirror: a word in MAPPED PINNED HOST memory (cudaHostAlloc; the pointer must be
+ * usable on the current device) that a failing attention kernel of the current device also writes
+ * its code to, next to the `status` word of the call.  A host that never synchronises can poll it
+ * between calls.  NULL switches the mirror off.  Kernels launched without a `status` word do not
+ * write it.  No counterpart in the reference.
+ *
  * Test hooks, for the failure-detection tests only (process-wide, not for production use; no
  * counterpart in the reference).  sage_test_set_wait_limit_us shortens the bound of every barrier
  * wait in the attention kernels (us <= 0 restores the default of about one second);
  * sage_test_drop_v_load(1) makes the TMA producer skip the V load of the first KV tile, so that a
  * wait runs out for real - it is honoured only while a shortened bound is set. */
+int sage_set_status_mirror(int* host_word);
 int sage_test_set_wait_limit_us(long long us);
 int sage_test_drop_v_load(int on);
 

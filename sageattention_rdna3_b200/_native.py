@@ -57,6 +57,8 @@ def load_abi() -> ctypes.CDLL:
     lib.sage_last_error.argtypes = []
     lib.sage_test_set_wait_limit_us.restype = i
     lib.sage_test_set_wait_limit_us.argtypes = [ctypes.c_longlong]
+    lib.sage_set_status_mirror.restype = i
+    lib.sage_set_status_mirror.argtypes = [vp]
     lib.sage_set_streamk.restype = i
     lib.sage_set_streamk.argtypes = [i]
     lib.sage_test_drop_v_load.restype = i

@@ -37,16 +37,21 @@ def _status_word(device: torch.device) -> torch.Tensor:
 
 
 def _status_mirror(device: torch.device):
-    """A pinned host copy of the device's status word (tensor, numpy view).  Every ``sageattn`` call
-    enqueues a 4-byte copy into it behind its kernels and looks at it before it launches: a kernel
-    that gave up is reported by the next call on that device at the latest, without any
-    synchronisation.  ``SAGEATTN_B200_STATUS_MIRROR=0`` switches the copy off."""
+    """A word in pinned host memory that a failing attention kernel of the device writes its code to
+    as well (tensor, numpy view; registered with ``sage_set_status_mirror``).  Every ``sageattn``
+    call looks at it before it launches: a kernel that gave up is reported by the next call on that
+    device, without any synchronisation and at no cost to calls that succeed.
+    ``SAGEATTN_B200_STATUS_MIRROR=0`` switches it off."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     pair = _status_mirrors.get(idx)
     if pair is None:
         host = torch.zeros(1, dtype=torch.int32).pin_memory()
         pair = (host, host.numpy())
         _status_mirrors[idx] = pair
+        with torch.cuda.device(idx):
+            rc = _native.load_abi().sage_set_status_mirror(host.data_ptr())
+        if rc != 0:
+            raise RuntimeError("sage_set_status_mirror failed: " + _native.load_abi().sage_last_error().decode())
     return pair
 
 
@@ -150,8 +155,8 @@ def sageattn(
     Errors on the device.  Every wait inside the kernels is bounded; a kernel that has to give up
     writes a code to a per-device status word and returns, leaving the output partly unwritten.  The
     call itself never synchronises, so it cannot raise for its own launch: the failure is raised by
-    the NEXT ``sageattn`` call on that device (the word is mirrored to pinned host memory behind
-    every call), by ``check_status()`` (synchronises), or at once with
+    the NEXT ``sageattn`` call on that device (a failing kernel also writes its code to a word in
+    pinned host memory), by ``check_status()`` (synchronises), or at once with
     ``SAGEATTN_B200_CHECK_STATUS=1`` (synchronises every call).  The reference has no such state.
     """
     dtype = q.dtype
@@ -220,16 +225,15 @@ def sageattn(
         # or the INT8 branch ([K mean,] quantise Q / K and convert a bf16 V in one launch, attention).
         direct = _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len)
         smooth = bool(smooth_k) and not direct          # the un-quantised branch has no use for the mean
-        mirror = None
         if _MIRROR_ON:
-            mirror, seen = _status_mirror(q.device)
+            _, seen = _status_mirror(q.device)
             if seen[0] != 0:                            # an earlier call on this device gave up
                 code = int(seen[0])
                 seen[0] = 0
                 _status_word(q.device).zero_()
                 raise RuntimeError(_STATUS_MESSAGE.format(code=code) + "; reported by the call after the one that failed")
         out = ops.sageattn_fwd(q, k, v, layout, int(is_causal), sm_scale, int(smooth), int(direct),
-                               _status_word(q.device), lse if want_lse else None, mirror)
+                               _status_word(q.device), lse if want_lse else None)
         o = out[0]
         if want_lse and smooth:
             # the kernel saw k - mean: every score of a row was lowered by sm_scale * q.mean

@@ -77,6 +77,7 @@ struct AttnParams {
   int32_t* s_dump;              // optional [B,Hq,Sq,Skv] int32 copy of Q.K^T (debug / parity)
   float* lse;                   // optional [B,Hq,Sq]: natural-log sum of exp of the scaled scores
   int* status;                  // optional device word, stays 0 on success
+  int* status_host;             // optional word in mapped pinned host memory that receives the same code
   long long wait_limit_cycles;  // bound of every barrier wait, in SM clocks
   int test_drop_v_load;         // test hook: the producer never loads V of the first KV tile
   // Persistent ("stream-K") variant only: the (query tile, KV tile) steps of the whole problem are
@@ -832,7 +833,14 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // A wait gave up.  Let copies and MMAs that are still in flight land before the shared memory
     // and TMEM of this CTA are handed back, then report.
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
-    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, *fail_code ? *fail_code : kStatusWaitTimeout);
+    if (threadIdx.x == 0) {
+      const int code = *fail_code ? *fail_code : kStatusWaitTimeout;
+      if (p.status) atomicCAS(p.status, 0, code);
+      if (p.status_host) {              // the host can see the failure without synchronising
+        *reinterpret_cast<volatile int*>(p.status_host) = code;
+        __threadfence_system();
+      }
+    }
     __syncthreads();
   }
   if (warp == 5) {

@@ -26,6 +26,7 @@ namespace {
 thread_local char g_err[512] = "";
 std::atomic<long long> g_wait_limit_cycles{sage::kWaitLimitCycles};
 std::atomic<int> g_test_drop_v_load{0};
+std::atomic<int*> g_status_host[64];      // per device: mapped pinned host word for failure codes (sage_set_status_mirror)
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -151,6 +152,11 @@ void fill_attn_params(sage::AttnParams* pp, void* o, int64_t o_stride_b, int64_t
   p.out_bf16 = (out_dtype == SAGE_DTYPE_BF16);
   p.lse = lse;
   p.status = status;
+  {
+    int dev = 0;
+    p.status_host = (status != nullptr && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64)
+                        ? g_status_host[dev].load(std::memory_order_relaxed) : nullptr;
+  }
   // Every barrier wait in the kernel gives up after this many SM clocks (about one second) and
   // reports through `status`.  The failure-detection test shortens the bound and makes one wait run
   // out on purpose through sage_test_set_wait_limit_us / sage_test_drop_v_load; the dropped load is
@@ -342,6 +348,13 @@ extern "C" {
 int sage_abi_version(void) { return SAGE_ABI_VERSION; }
 const char* sage_last_error(void) { return g_err; }
 
+int sage_set_status_mirror(int* host_word) {
+  int dev = 0;
+  SAGE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SAGE_ERR_INVALID, "device index %d is out of range", dev);
+  g_status_host[dev].store(host_word, std::memory_order_relaxed);
+  return SAGE_OK;
+}
 int sage_test_set_wait_limit_us(long long us) {
   g_wait_limit_cycles.store(us > 0 ? us * 2000 : sage::kWaitLimitCycles, std::memory_order_relaxed);   // ~2 GHz
   return SAGE_OK;

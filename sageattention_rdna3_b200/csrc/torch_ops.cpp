@@ -326,31 +326,9 @@ at::Tensor bf16_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor&
 // fp16_attn / bf16_attn) or the INT8 branch (:165-198: [mean,] quantise, attention).  Returns
 // [output] or, with smooth_k on the INT8 branch, [output, key_mean] (the caller needs the mean to
 // refer a log-sum-exp to the original keys).  One Python -> C++ crossing instead of two to four.
-// `status_host` (optional, one pinned int32): the status word is copied there behind the kernels, so
-// the caller can look at it later without synchronising.
-std::vector<at::Tensor> sageattn_fwd_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
-                                          int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
-                                          const at::Tensor& status, const c10::optional<at::Tensor>& lse);
-
 std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
                                      int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
-                                     const at::Tensor& status, const c10::optional<at::Tensor>& lse,
-                                     const c10::optional<at::Tensor>& status_host) {
-  std::vector<at::Tensor> out = sageattn_fwd_impl(q, k, v, layout, is_causal, sm_scale, smooth_k, use_direct, status, lse);
-  if (status_host.has_value()) {
-    TORCH_CHECK(status_host->is_pinned() && status_host->scalar_type() == at::kInt && status_host->numel() >= 1,
-                "status_host must be a pinned int32 host tensor");
-    c10::cuda::CUDAGuard guard(q.device());
-    const cudaError_t e = cudaMemcpyAsync(status_host->data_ptr(), status.data_ptr(), sizeof(int), cudaMemcpyDeviceToHost,
-                                          static_cast<cudaStream_t>(current_stream(q)));
-    TORCH_CHECK(e == cudaSuccess, "copy of the status word failed: ", cudaGetErrorString(e));
-  }
-  return out;
-}
-
-std::vector<at::Tensor> sageattn_fwd_impl(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
-                                          int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
-                                          const at::Tensor& status, const c10::optional<at::Tensor>& lse) {
+                                     const at::Tensor& status, const c10::optional<at::Tensor>& lse) {
   at::Tensor o = at::empty_like(q);
   const bool bf16 = q.scalar_type() == at::kBFloat16;
   const c10::optional<at::Tensor> st(status), none;
@@ -409,7 +387,7 @@ void fold_partial(at::Tensor& o_acc, at::Tensor& lse_acc, const at::Tensor& o_pa
 TORCH_LIBRARY(sageattention, m) {
   m.def("fold_partial(Tensor(a!) o_acc, Tensor(b!) lse_acc, Tensor o_part, Tensor lse_part, int tensor_layout, int first) -> ()");
   m.def("sageattn_fwd(Tensor query, Tensor key, Tensor value, int tensor_layout, int is_causal, float sm_scale, "
-        "int smooth_k, int use_direct, Tensor status, Tensor? lse=None, Tensor? status_host=None) -> Tensor[]");
+        "int smooth_k, int use_direct, Tensor status, Tensor? lse=None) -> Tensor[]");
   m.def("fp16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
         "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("bf16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
