@@ -403,13 +403,20 @@ def test_host_pipeline_matches_device_call(dev, monkeypatch, layout):
     q, k, v = (H.randn(shp(h), s, torch.bfloat16).pin_memory() for s, h in ((0, Hq), (1, Hkv), (2, Hkv)))
     kw = dict(tensor_layout=layout, is_causal=True, smooth_k=True)
     H.set_streamk(0)
-    got = sageattn_host(q, k, v, device=dev, chunks=5, **kw)
-    torch.cuda.synchronize()
     want = sageattn(q.to(dev), k.to(dev), v.to(dev), **kw).cpu()
-    assert torch.equal(got, want)
-    H.set_streamk(-1)
-    got = sageattn_host(q, k, v, device=dev, chunks=5, **kw)
     torch.cuda.synchronize()
+    # the returned host tensor is read at once, with no synchronisation by the caller: the call
+    # itself waits for its last device-to-host copy
+    got = sageattn_host(q, k, v, device=dev, chunks=5, **kw).clone()
+    assert torch.equal(got, want)
+    # wait=False returns before the copies have landed, with the event that says when they have
+    out = torch.full(q.shape, float("nan"), dtype=q.dtype).pin_memory()
+    res, event = sageattn_host(q, k, v, out=out, device=dev, chunks=5, wait=False, **kw)
+    assert res is out and event is not None
+    event.synchronize()
+    assert torch.equal(out, want)
+    H.set_streamk(-1)
+    got = sageattn_host(q, k, v, device=dev, chunks=5, **kw).clone()
     check_status(dev)
     assert (got.float() - want.float()).abs().max().item() <= 2 ** -5
 
