@@ -99,6 +99,8 @@ SMOOTH_CASES = [
     # B, Hq, Hkv, Sq, Skv, D, dtype, layout, k_offset
     (2, 8, 8, 8192, 8192, 128, torch.bfloat16, "HND", 2.5),      # B=2 H=32 S=8192 D=128 with fewer heads
     (1, 40, 40, 1024, 1024, 128, torch.bfloat16, "HND", 1.0),    # more heads than clusters: several heads per cluster
+    (2, 32, 32, 8192, 8192, 128, torch.bfloat16, "HND", 2.0),    # 64 heads of 2 MiB: more than three heads per cluster
+    (3, 7, 7, 777, 1234, 64, torch.float16, "NHD", 0.7),         # 21 heads, ragged, head_dim 64
     (1, 4, 2, 1000, 3001, 64, torch.float16, "NHD", -1.5),       # head_dim 64, ragged, GQA, cross lengths
     (2, 3, 3, 33, 65, 128, torch.float16, "NHD", 0.5),
     (1, 2, 1, 300, 1, 64, torch.bfloat16, "HND", 3.0),           # a single key
