@@ -254,6 +254,9 @@ def test_config3_full_size_properties_and_sampled_units(dev, monkeypatch):
     off = torch.rand((1, Hh, 1, D), generator=g) * 8.0 - 4.0
     k = (torch.randn((B, Hh, S, D), generator=g) + off).to(torch.bfloat16)
     v = torch.randn((B, Hh, S, D), generator=g).to(torch.bfloat16)
+    # property (3) doubles V: keep V out of the fp16 subnormal range, where v -> fp16 -> * 2 and
+    # 2v -> fp16 round differently (V goes through fp16) and exact linearity would hold only by luck
+    v = torch.where(v.abs() < 2.0 ** -13, torch.full_like(v, 2.0 ** -13), v)
     kw = dict(tensor_layout="HND", is_causal=True, smooth_k=True)
     qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
     from sageattention_rdna3_b200 import check_status, sageattn
