@@ -15,7 +15,9 @@ of V; fused attention) over one batch of synthetic input of the named workload. 
 * ``e2e``       - the same metric through ``sageattn_host()`` with HOST (pinned) q, k, v and a host
                   output: the copies in both directions are inside the timed region; ``copy_floor_ms``
                   is the same bytes copied with no compute.
-* ``allgather`` - N > 1: the step with the final NCCL all-gather of the outputs, serial and overlapped.
+* ``allgather`` - N > 1: the step with the final all-gather of the outputs: NCCL after the step (serial),
+                  NCCL on a side stream under the next step (overlapped), and written by the attention
+                  kernel itself into every rank's copy over NVLink (fused).
 * ``configs``   - N = 1: step time / TOPS / roofline fraction of the other benchmark configurations.
 * ``cpu_baseline`` - the CPU oracle (a port of the reference's arithmetic) on the host cores, on a
                   bounded sample of the same workload.
@@ -264,8 +266,9 @@ class Problem:
         e.record()
         return e
 
-    def step_ops(self, record=False, o=None):
-        """The hot path as its operators, optionally with CUDA events around each kernel."""
+    def step_ops(self, record=False, o=None, peers=None):
+        """The hot path as its operators, optionally with CUDA events around each kernel.  ``peers``:
+        addresses of further copies of ``o`` (other GPUs' memory) that the attention kernel writes too."""
         w, ops = self.w, self.ops
         o = self.o if o is None else o
         bf16 = self.q.dtype == torch.bfloat16
@@ -286,7 +289,7 @@ class Problem:
             e0 = self._ev()
             self.prep_events.append((p0, e0))
         ops.qk_int8_sv_f16_attn(q8, k8, v16, o, qs, ks, self.layout_code, int(w["causal"]), self.sm_scale,
-                                value_layout=vl, status=self.status)
+                                value_layout=vl, status=self.status, peer_ptrs=peers)
         if record:
             self.attn_events.append((e0, self._ev()))
         return o
@@ -393,6 +396,26 @@ def measure_gather(prob, steps, warmup, barrier, world, dist, sizes):
             drain()
 
     res["overlapped_ms"] = timed(overlapped_all, steps, barrier)
+
+    # The gather inside the attention launch: the epilogue writes every finished tile into all ranks'
+    # copies of the output (mapped peer memory, ordinary stores); a one-element all-reduce follows.
+    # Two sets of buffers, used alternately, so that no rank writes into a copy that another rank
+    # may still be reading from the step before.
+    from sageattention_rdna3_b200.peer_gather import PeerOutput
+    peer_sets = [PeerOutput(sizes, unit_shape, prob.o.dtype, dev) for _ in range(2)]
+
+    def fused(i):
+        po = peer_sets[i & 1]
+        if prob.units > 0:
+            prob.step_ops(o=po.local_slab(), peers=po.scatter_addresses())
+        po.sync()
+        finish(po.full)
+
+    for i in range(warmup):
+        fused(i)
+    res["fused_ms"] = timed(fused, steps, barrier)
+    for po in peer_sets:
+        po.close()
     elem = prob.o.element_size()
     per_unit = elem
     for d in unit_shape:
@@ -577,9 +600,9 @@ def main():
 
     MAX, SUM = dist.ReduceOp.MAX, dist.ReduceOp.SUM
     g = gather or {}
-    ms_public, ms_ops, attn_ms_max, ser_ms, ovl_ms, alone_ms, e2e_ms, floor_ms = over_ranks(
+    ms_public, ms_ops, attn_ms_max, ser_ms, ovl_ms, alone_ms, e2e_ms, floor_ms, fused_ms = over_ranks(
         [ms_public, ms_ops, attn_ms, g.get("serial_ms", 0.0), g.get("overlapped_ms", 0.0), g.get("gather_alone_ms", 0.0),
-         e2e["ms"] if e2e else 0.0, e2e["copy_floor_ms"] if e2e else 0.0], MAX)
+         e2e["ms"] if e2e else 0.0, e2e["copy_floor_ms"] if e2e else 0.0, g.get("fused_ms", 0.0)], MAX)
     total_nominal, total_executed, h2d_total, d2h_total = over_ranks(
         [prob.nominal, prob.executed, e2e["h2d"] if e2e else 0.0, e2e["d2h"] if e2e else 0.0], SUM)
 
@@ -616,6 +639,10 @@ def main():
                 "serial": {"ms_per_step": ser_ms, "value": tops(ser_ms)},
                 "overlapped": {"ms_per_step": ovl_ms, "value": tops(ovl_ms),
                                "how": "gather of step i on a side stream while step i+1 computes (two output buffers)"},
+                "fused": {"ms_per_step": fused_ms, "value": tops(fused_ms),
+                          "how": "no gather collective: the attention kernel's epilogue writes every finished tile into "
+                                 "all ranks' copies of the output (mapped peer memory, ordinary stores over NVLink), then "
+                                 "a one-element all-reduce; one stream, two sets of buffers used alternately"},
             }
         if e2e:
             line["e2e"] = {"value": tops(e2e_ms), "unit": "TOPS", "h2d_bytes_per_step": int(h2d_total),

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SAGE_ABI_VERSION 6
+#define SAGE_ABI_VERSION 7
 
 #define SAGE_DTYPE_F16 0
 #define SAGE_DTYPE_BF16 1
@@ -144,6 +144,33 @@ int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sa
                                 const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
                                 int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* workspace,
                                 int64_t workspace_bytes, void* stream);
+
+/* Attention whose output is also scattered to the other GPUs of the node, for the all-gather that
+ * follows when (batch, kv-head) units are sharded over GPUs.
+ * No counterpart in the reference (single GPU).  As sage_qk_int8_sv_f16_attn_lse, and every finished
+ * 32-row piece of the output is written, with ordinary 16-byte stores from the epilogue, to n_peers
+ * (0..SAGE_MAX_PEERS) further buffers peer_o[i] as well: device addresses, normally in the memory of
+ * other GPUs (sage_peer_open), each with the layout and strides of `o` - the caller passes the
+ * address of THIS rank's slice inside every peer's copy of the gathered output.  The transfer thus
+ * runs under the computation, tile by tile.  The stores are complete when the launch is (stream
+ * order); the peers learn of that through whatever cross-rank synchronisation the caller uses after
+ * it (an all-reduce of one element is enough).  Always the plain launch; no s_dump. */
+#define SAGE_MAX_PEERS 15
+int sage_qk_int8_sv_f16_attn_scatter(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                                     const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                                     int D, int is_causal, float* lse, int* status, int n_peers, void* const* peer_o,
+                                     void* stream);
+
+/* Mapping of a device buffer that another process of the node owns (one process per GPU).
+ * No counterpart in the reference.  sage_peer_export, in the owner: the 64-byte CUDA IPC handle of the
+ * allocation that contains `ptr` (memory from cudaMalloc, which is what PyTorch's default allocator
+ * hands out) and the offset of `ptr` in it.  sage_peer_open, in another process with its own GPU
+ * current: maps the allocation and returns the address that corresponds to `ptr`; peer access from
+ * the current device is enabled by the call.  sage_peer_close undoes one open. */
+int sage_peer_export(const void* ptr, unsigned char handle[64], int64_t* offset);
+int sage_peer_open(const unsigned char handle[64], int64_t offset, void** mapped);
+int sage_peer_close(void* mapped, int64_t offset);
 
 /* Un-quantised attention for short sequences: O = softmax2(sm_scale*log2(e) * Q K^T) V with Q and K
  * in fp16 or bf16 as the caller holds them.

@@ -158,6 +158,11 @@ def sageattn(
     the NEXT ``sageattn`` call on that device (a failing kernel also writes its code to a word in
     pinned host memory), by ``check_status()`` (synchronises), or at once with
     ``SAGEATTN_B200_CHECK_STATUS=1`` (synchronises every call).  The reference has no such state.
+
+    Two keywords beyond the reference's, used by the multi-GPU paths: ``out`` (a tensor with the
+    shape, dtype and device of ``q``; fp16 / bf16 inputs only) receives the result instead of a new
+    tensor, and ``scatter_to`` (device addresses of further copies of ``out``, normally in other
+    GPUs' memory, see :mod:`.peer_gather`; INT8 kernel only) makes the kernel write them as well.
     """
     dtype = q.dtype
     assert q.is_cuda, "Input tensors must be on CUDA/HIP device."
@@ -209,6 +214,13 @@ def sageattn(
 
     o = None
     lse = None
+    out_arg, scatter_to = kwargs.get("out"), kwargs.get("scatter_to")
+    if out_arg is not None:
+        assert input_dtype != torch.float32, "out= is for fp16 / bf16 inputs."
+        assert out_arg.shape == q.shape and out_arg.dtype == q.dtype and out_arg.device == q.device, (
+            "out must have the shape, dtype and device of q."
+        )
+    assert not scatter_to or out_arg is not None, "scatter_to needs out=."
     want_lse = return_lse and os.environ.get("SAGEATTN_B200_LSE_ZEROS", "0") != "1"
     if return_lse:
         lse_shape = (q_shape[0], q_shape[head_dim_idx], q_len)
@@ -217,13 +229,15 @@ def sageattn(
         else:
             lse = torch.zeros(lse_shape, dtype=torch.float32, device=q.device)
     if q_len == 0 or q_shape[0] == 0 or q_shape[head_dim_idx] == 0:
-        o = torch.empty_like(q)
-    elif kv_len == 0:
-        o = torch.zeros_like(q)          # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
+        o = torch.empty_like(q) if out_arg is None else out_arg
+    elif kv_len == 0 and not scatter_to:
+        # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
+        o = torch.zeros_like(q) if out_arg is None else out_arg.zero_()
     else:
         # core.py:141-198 in one operator call: the un-quantised branch (V as fp16, fp16_attn / bf16_attn)
         # or the INT8 branch ([K mean,] quantise Q / K and convert a bf16 V in one launch, attention).
         direct = _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len)
+        assert not (direct and scatter_to), "scatter_to is served by the INT8 kernel only (pass kernel='int8')."
         smooth = bool(smooth_k) and not direct          # the un-quantised branch has no use for the mean
         if _MIRROR_ON:
             _, seen = _status_mirror(q.device)
@@ -233,7 +247,8 @@ def sageattn(
                 _status_word(q.device).zero_()
                 raise RuntimeError(_STATUS_MESSAGE.format(code=code) + "; reported by the call after the one that failed")
         out = ops.sageattn_fwd(q, k, v, layout, int(is_causal), sm_scale, int(smooth), int(direct),
-                               _status_word(q.device), lse if want_lse else None)
+                               _status_word(q.device), lse if want_lse else None, out_arg,
+                               [int(a) for a in scatter_to] if scatter_to else None)
         o = out[0]
         if want_lse and smooth:
             # the kernel saw k - mean: every score of a row was lowered by sm_scale * q.mean

@@ -62,6 +62,7 @@ enum AttnStatus : int {
   kStatusWaitTimeout = 2,       // + 16 * (id of the barrier the wait gave up on)
 };
 
+constexpr int kMaxPeers = 15;
 struct AttnParams {
   const float* q_scale;         // [B,Hq,q_groups]
   const float* k_scale;         // [B,Hkv,k_groups]
@@ -87,6 +88,11 @@ struct AttnParams {
   int sk_nkv_full;              // ceil(Skv / 128)
   float* part_o;                // [gridDim.x][2][128][D] fp32: acc / l of a span that covers part of an item
   float* part_lse;              // [gridDim.x][2][128] fp32: m + log2 l of the same (base 2)
+  // Output scatter (plain launch only): every finished tile is also written, with ordinary 16-byte
+  // stores, to `n_peers` more buffers that have the layout and strides of `o` - the same slice of the
+  // gathered output in the memory of the other GPUs of the node.
+  int n_peers;
+  void* peer_o[kMaxPeers];
 };
 
 // QKB = bytes per element of Q and K in shared memory: 1 (int8) or 2 (fp16 / bf16, the
@@ -804,6 +810,26 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (whole) fence_proxy_async_smem();
       __syncwarp();
+      if (!STREAMK && p.n_peers > 0) {
+        // The staged rows go to the peers as well: 8 lanes cover the 128 bytes of one row of a box
+        // (undoing the swizzle), so a warp instruction writes four rows of 128 contiguous bytes.
+        const int sub = lane >> 3, piece = lane & 7;
+#pragma unroll
+        for (int bx = 0; bx < D / 64; ++bx) {
+#pragma unroll
+          for (int rr = 0; rr < 8; ++rr) {
+            const int r = rr * 4 + sub;
+            const int row_g = q_base + warp * 32 + r;
+            const uint4 val = *reinterpret_cast<const uint4*>(stage + bx * 4096 + r * 128 + ((piece ^ (r & 7)) * 16));
+            if (row_g < p.Sq) {
+              const long long off = b * p.o_stride_b + hq * p.o_stride_h + static_cast<long long>(row_g) * p.o_stride_s +
+                                    bx * 64 + piece * 8;                     // in 16-bit elements
+              for (int pe = 0; pe < p.n_peers; ++pe)
+                *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.peer_o[pe]) + off) = val;
+            }
+          }
+        }
+      }
       if (lane == 0) {
         if (whole && q_base + warp * 32 < p.Sq) {
 #pragma unroll

@@ -568,11 +568,89 @@ int64_t sage_attn_workspace_bytes(int B, int Hq, int Sq, int Skv, int D, int is_
   return plan.use ? static_cast<int64_t>(plan.workspace_bytes) : 0;
 }
 
+namespace {
+int attn_int8_impl(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o, int64_t o_stride_b,
+                   int64_t o_stride_h, int64_t o_stride_s, const float* q_scale, const float* k_scale, int out_dtype,
+                   int B, int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float* lse, int32_t* s_dump,
+                   int* status, void* workspace, int64_t workspace_bytes, int n_peers, void* const* peer_o, void* stream);
+}  // namespace
+
 int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
                                 int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
                                 const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
                                 int D, int is_causal, float* lse, int32_t* s_dump, int* status, void* workspace,
                                 int64_t workspace_bytes, void* stream) {
+  return attn_int8_impl(q_i8, k_i8, v16, o, o_stride_b, o_stride_h, o_stride_s, q_scale, k_scale, out_dtype, B, Hq, Hkv,
+                        Sq, Skv, D, is_causal, lse, s_dump, status, workspace, workspace_bytes, 0, nullptr, stream);
+}
+
+int sage_qk_int8_sv_f16_attn_scatter(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o,
+                                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, const float* q_scale,
+                                     const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
+                                     int D, int is_causal, float* lse, int* status, int n_peers, void* const* peer_o,
+                                     void* stream) {
+  SAGE_REQUIRE(n_peers >= 0 && n_peers <= sage::kMaxPeers, "sage_qk_int8_sv_f16_attn_scatter: n_peers must be 0..%d, got %d",
+               sage::kMaxPeers, n_peers);
+  SAGE_REQUIRE(n_peers == 0 || peer_o != nullptr, "sage_qk_int8_sv_f16_attn_scatter: null peer list");
+  for (int i = 0; i < n_peers; ++i) {
+    SAGE_REQUIRE(peer_o[i] != nullptr && aligned16(peer_o[i]) && peer_o[i] != o,
+                 "sage_qk_int8_sv_f16_attn_scatter: peer buffer %d must be a 16-byte aligned address other than o", i);
+  }
+  return attn_int8_impl(q_i8, k_i8, v16, o, o_stride_b, o_stride_h, o_stride_s, q_scale, k_scale, out_dtype, B, Hq, Hkv,
+                        Sq, Skv, D, is_causal, lse, nullptr, status, nullptr, 0, n_peers, peer_o, stream);
+}
+
+// Mapping of another process's device buffer (one process per GPU on one node): the owner exports
+// the CUDA IPC handle of the allocation that holds `ptr` and the offset of `ptr` inside it, the
+// others open it.  Peer access from the current device is enabled by the open.
+int sage_peer_export(const void* ptr, unsigned char handle[64], int64_t* offset) {
+  SAGE_REQUIRE(ptr != nullptr && handle != nullptr && offset != nullptr, "sage_peer_export: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  // (taken from the driver at run time, like the tensor-map encoder: the library links the runtime only)
+  using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range_fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      range_fn = reinterpret_cast<RangeFn>(sym);
+    }
+  });
+  if (range_fn == nullptr) return fail(SAGE_ERR_CUDA, "cuMemGetAddressRange is not available from the driver");
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult cr = range_fn(&base, &size, reinterpret_cast<CUdeviceptr>(ptr));
+  SAGE_REQUIRE(cr == CUDA_SUCCESS, "sage_peer_export: not a device allocation (driver error %d)", static_cast<int>(cr));
+  cudaIpcMemHandle_t h;
+  SAGE_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  memcpy(handle, &h, 64);
+  *offset = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return SAGE_OK;
+}
+
+int sage_peer_open(const unsigned char handle[64], int64_t offset, void** mapped) {
+  SAGE_REQUIRE(handle != nullptr && mapped != nullptr && offset >= 0, "sage_peer_open: bad argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* base = nullptr;
+  SAGE_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  *mapped = static_cast<unsigned char*>(base) + offset;
+  return SAGE_OK;
+}
+
+int sage_peer_close(void* mapped, int64_t offset) {
+  SAGE_REQUIRE(mapped != nullptr && offset >= 0, "sage_peer_close: bad argument");
+  SAGE_CUDA(cudaIpcCloseMemHandle(static_cast<unsigned char*>(mapped) - offset));
+  return SAGE_OK;
+}
+
+namespace {
+int attn_int8_impl(const int8_t* q_i8, const int8_t* k_i8, const sage_strided_t* v16, void* o, int64_t o_stride_b,
+                   int64_t o_stride_h, int64_t o_stride_s, const float* q_scale, const float* k_scale, int out_dtype,
+                   int B, int Hq, int Hkv, int Sq, int Skv, int D, int is_causal, float* lse, int32_t* s_dump,
+                   int* status, void* workspace, int64_t workspace_bytes, int n_peers, void* const* peer_o, void* stream) {
   SAGE_REQUIRE(q_i8 && v16 && o && q_scale, "sage_qk_int8_sv_f16_attn: null pointer");
   SAGE_REQUIRE(Skv == 0 || (k_i8 && v16->ptr && k_scale), "sage_qk_int8_sv_f16_attn: null pointer");
   SAGE_REQUIRE(out_dtype == SAGE_DTYPE_F16 || out_dtype == SAGE_DTYPE_BF16,
@@ -592,6 +670,8 @@ int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sa
   fill_attn_params(&p, o, o_stride_b, o_stride_h, o_stride_s, out_dtype, B, Hq, Hkv, Sq, Skv, lse, status);
   p.q_scale = q_scale; p.k_scale = k_scale;
   p.s_dump = s_dump;
+  p.n_peers = n_peers;                                  // (the persistent launch does not scatter: plain launch)
+  for (int i = 0; i < n_peers; ++i) p.peer_o[i] = peer_o[i];
 
   // With no keys every row has l == 0 and the output is 0 (csrc/attn_gfx11.cu:771).  The kernel
   // handles that without touching K or V, but a tensor map cannot have a zero extent: describe one
@@ -626,7 +706,7 @@ int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sa
     if (rc) return rc;
   }
   const bool dump = (s_dump != nullptr);
-  if (workspace != nullptr && !dump) {
+  if (workspace != nullptr && !dump && n_peers == 0) {
     StreamKPlan plan;
     int rc = plan_streamk(&plan, B, Hq, Sq, Skv, D, is_causal);
     if (rc) return rc;
@@ -646,6 +726,7 @@ int sage_qk_int8_sv_f16_attn_ws(const int8_t* q_i8, const int8_t* k_i8, const sa
   return is_causal ? SAGE_LAUNCH(64, true) : SAGE_LAUNCH(64, false);
 #undef SAGE_LAUNCH
 }
+}  // namespace
 
 int sage_fold_attn_partial(const sage_strided_t* o_acc, float* lse_acc, int64_t lse_stride_b, int64_t lse_stride_h,
                            const sage_strided_t* o_part, int part_dtype, const float* lse_part, int B, int H, int S, int D,

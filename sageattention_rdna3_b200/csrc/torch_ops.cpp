@@ -195,17 +195,20 @@ at::Tensor v_to_f16(const at::Tensor& v, int64_t layout) {
 
 // qk_int8_sv_f16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor q_scale,
 //                     Tensor k_scale, int tensor_layout, int is_causal, float sm_scale, *,
-//                     int value_layout=-1, Tensor? s_dump, Tensor? status, Tensor? lse) -> Tensor
+//                     int value_layout=-1, Tensor? s_dump, Tensor? status, Tensor? lse,
+//                     int[]? peer_ptrs) -> Tensor
 // Counterpart of qk_int8_sv_bf16_attn_t (csrc/pybind_gfx11.cpp:19-23), call-compatible with its nine
 // positional arguments: query/key are the int8 [B,H,S,D] tensors from quant_qk_int8; `value` is fp16
 // in `value_layout` (keyword; -1 = the same as `tensor_layout`); `output` is fp16/bf16 in
 // `tensor_layout`.  sm_scale is already folded into q_scale and is accepted for signature parity.
 // `lse` (optional, fp32 [B,Hq,Sq]) receives the natural-log sum of exponentials of every row.
+// `peer_ptrs` (optional): device addresses of further copies of `output` (same layout and strides,
+// normally in other GPUs' memory) that the kernel writes as well (sage_qk_int8_sv_f16_attn_scatter).
 at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, const at::Tensor& v, at::Tensor& o,
                                const at::Tensor& q_scale, const at::Tensor& k_scale, int64_t layout,
                                int64_t is_causal, double /*sm_scale*/, int64_t value_layout,
                                const c10::optional<at::Tensor>& s_dump, const c10::optional<at::Tensor>& status,
-                               const c10::optional<at::Tensor>& lse) {
+                               const c10::optional<at::Tensor>& lse, at::OptionalIntArrayRef peer_ptrs) {
   TORCH_CHECK(q_i8.is_cuda() && q_i8.scalar_type() == at::kChar && q_i8.is_contiguous() && q_i8.dim() == 4,
               "query must be a contiguous int8 CUDA tensor [B,Hq,Sq,D]");
   TORCH_CHECK(k_i8.scalar_type() == at::kChar && k_i8.is_contiguous() && k_i8.dim() == 4,
@@ -246,6 +249,18 @@ at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, c
   c10::cuda::CUDAGuard guard(q_i8.device());
   const sage_strided_t vs = strided_of(v, value_layout);
   const sage_strided_t os = strided_of(o, layout);
+  if (peer_ptrs.has_value() && !peer_ptrs->empty()) {
+    TORCH_CHECK(!dump_ptr, "peer_ptrs and s_dump cannot be combined");
+    std::vector<void*> peers;
+    for (int64_t a : *peer_ptrs) peers.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(a)));
+    check_rc(sage_qk_int8_sv_f16_attn_scatter(q_i8.data_ptr<int8_t>(), k_i8.data_ptr<int8_t>(), &vs, o.data_ptr(),
+                                              os.stride_b, os.stride_h, os.stride_s, q_scale.data_ptr<float>(),
+                                              k_scale.data_ptr<float>(), dtype_code(o), (int)B, (int)Hq, (int)Hkv,
+                                              (int)Sq, (int)Skv, (int)D, (int)is_causal, lse_ptr, status_ptr,
+                                              (int)peers.size(), peers.data(), current_stream(q_i8)),
+             "qk_int8_sv_f16_attn");
+    return o;
+  }
   // Problems that would fill the GPU unevenly run on persistent CTAs and need scratch for partial results.
   at::Tensor workspace;
   const int64_t ws_bytes = dump_ptr ? 0 : sage_attn_workspace_bytes((int)B, (int)Hq, (int)Sq, (int)Skv, (int)D, (int)is_causal);
@@ -320,7 +335,7 @@ at::Tensor bf16_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor&
 }
 
 // sageattn_fwd(Tensor query, Tensor key, Tensor value, int tensor_layout, int is_causal, float sm_scale,
-//              int smooth_k, int use_direct, Tensor status, Tensor? lse) -> Tensor[]
+//              int smooth_k, int use_direct, Tensor status, Tensor? lse, Tensor? out, int[]? peer_ptrs) -> Tensor[]
 // The whole of the reference's sageattn body after its assertions (sageattention/core.py:96-201) in
 // one operator call: allocate the output, then either the un-quantised branch (:141-163: fp16 V,
 // fp16_attn / bf16_attn) or the INT8 branch (:165-198: [mean,] quantise, attention).  Returns
@@ -328,8 +343,18 @@ at::Tensor bf16_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor&
 // refer a log-sum-exp to the original keys).  One Python -> C++ crossing instead of two to four.
 std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t layout,
                                      int64_t is_causal, double sm_scale, int64_t smooth_k, int64_t use_direct,
-                                     const at::Tensor& status, const c10::optional<at::Tensor>& lse) {
-  at::Tensor o = at::empty_like(q);
+                                     const at::Tensor& status, const c10::optional<at::Tensor>& lse,
+                                     const c10::optional<at::Tensor>& out, at::OptionalIntArrayRef peer_ptrs) {
+  at::Tensor o;
+  if (out.has_value()) {
+    TORCH_CHECK(out->sizes() == q.sizes() && out->scalar_type() == q.scalar_type() && out->device() == q.device(),
+                "out must have the shape, dtype and device of query");
+    o = *out;
+  } else {
+    o = at::empty_like(q);
+  }
+  TORCH_CHECK(!(use_direct && peer_ptrs.has_value() && !peer_ptrs->empty()),
+              "peer_ptrs is only served by the INT8 kernel");
   const bool bf16 = q.scalar_type() == at::kBFloat16;
   const c10::optional<at::Tensor> st(status), none;
   if (use_direct) {
@@ -347,13 +372,13 @@ std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, c
     std::vector<at::Tensor> parts =
         prep_smooth_qkv(q, k, bf16 ? c10::optional<at::Tensor>(v) : c10::optional<at::Tensor>(), layout, sm_scale);
     qk_int8_sv_f16_attn(parts[0], parts[2], bf16 ? parts[5] : v, o, parts[1], parts[3], layout, is_causal, sm_scale,
-                        bf16 ? kHND : layout, none, st, lse);
+                        bf16 ? kHND : layout, none, st, lse, peer_ptrs);
     return {o, parts[4]};
   }
   at::Tensor k_mean = smooth_k ? mean_seq(k, layout) : at::empty({0}, q.options());
   std::vector<at::Tensor> parts = quant_impl(q, k, k_mean, bf16 ? &v : nullptr, layout, sm_scale);
   qk_int8_sv_f16_attn(parts[0], parts[2], bf16 ? parts[4] : v, o, parts[1], parts[3], layout, is_causal, sm_scale,
-                      bf16 ? kHND : layout, none, st, lse);
+                      bf16 ? kHND : layout, none, st, lse, peer_ptrs);
   if (smooth_k) return {o, k_mean};
   return {o};
 }
@@ -387,14 +412,14 @@ void fold_partial(at::Tensor& o_acc, at::Tensor& lse_acc, const at::Tensor& o_pa
 TORCH_LIBRARY(sageattention, m) {
   m.def("fold_partial(Tensor(a!) o_acc, Tensor(b!) lse_acc, Tensor o_part, Tensor lse_part, int tensor_layout, int first) -> ()");
   m.def("sageattn_fwd(Tensor query, Tensor key, Tensor value, int tensor_layout, int is_causal, float sm_scale, "
-        "int smooth_k, int use_direct, Tensor status, Tensor? lse=None) -> Tensor[]");
+        "int smooth_k, int use_direct, Tensor status, Tensor? lse=None, Tensor? out=None, int[]? peer_ptrs=None) -> Tensor[]");
   m.def("fp16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
         "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("bf16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, int tensor_layout, int value_layout, "
         "int is_causal, float sm_scale, int bm_sel=0, Tensor? status=None, Tensor? lse=None) -> Tensor");
   m.def("qk_int8_sv_f16_attn(Tensor query, Tensor key, Tensor value, Tensor(a!) output, Tensor q_scale, "
         "Tensor k_scale, int tensor_layout, int is_causal, float sm_scale, *, int value_layout=-1, "
-        "Tensor? s_dump=None, Tensor? status=None, Tensor? lse=None) -> Tensor");
+        "Tensor? s_dump=None, Tensor? status=None, Tensor? lse=None, int[]? peer_ptrs=None) -> Tensor");
   m.def("quant_qk_int8(Tensor query, Tensor key, Tensor key_mean, int tensor_layout, float sm_scale) -> Tensor[]");
   m.def("prep_qkv(Tensor query, Tensor key, Tensor value, Tensor key_mean, int tensor_layout, float sm_scale) "
         "-> Tensor[]");

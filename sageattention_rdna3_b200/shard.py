@@ -72,8 +72,8 @@ def from_units(o_units: torch.Tensor, batch: int, num_qo_heads: int, tensor_layo
 
 def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                      is_causal: bool = False, sm_scale: Optional[float] = None, smooth_k: bool = False,
-                     group=None, gather: bool = True, attn_fn: Optional[Callable] = None,
-                     global_heads: Optional[tuple] = None, **kwargs):
+                     group=None, gather=True, attn_fn: Optional[Callable] = None,
+                     global_heads: Optional[tuple] = None, peer_output=None, **kwargs):
     """Run this rank's share of ``sageattn(q, k, v)`` and optionally all-gather the outputs.
 
     Two ways to pass the inputs.  Global: every rank passes the same global ``q, k, v`` in
@@ -85,6 +85,12 @@ def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_l
     otherwise this rank's units ``[n, Hq/Hkv, Sq, D]`` and its :class:`Shard`.  ``attn_fn`` defaults to :func:`sageattn`; other
     keyword arguments go to it.  The choice between the INT8 and the un-quantised kernel is made
     here, from the caller's shapes and layout, so that every rank and the unsharded call agree.
+
+    ``gather="fused"`` with ``peer_output`` (a :class:`.peer_gather.PeerOutput` built once for these
+    shapes): the attention kernel writes this rank's slab into every rank's copy of the output while
+    it computes, and the collective shrinks to a one-element all-reduce.  The result is a view of
+    ``peer_output.full`` (valid until the next call that uses the same ``peer_output``).  Calls that
+    the un-quantised kernel serves fall back to the all-gather.
     """
     import torch.distributed as dist
     if attn_fn is None:
@@ -114,6 +120,20 @@ def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_l
         from .core import use_direct_kernel
         direct = use_direct_kernel(q.size(-1), tensor_layout, is_causal, q_len, kv_len)
         kwargs["kernel"] = "direct" if direct else "int8"
+    if gather == "fused" and world > 1 and kwargs["kernel"] == "int8":
+        if peer_output is None:
+            raise ValueError('gather="fused" needs peer_output=PeerOutput(...)')
+        rep = hq // hkv
+        want = (B * hkv, rep, ql.size(2), ql.size(3))
+        if tuple(peer_output.full.shape) != want or peer_output.full.dtype != ql.dtype or \
+                peer_output.unit_sizes != [s.n_units for s in shards]:
+            raise ValueError(f"peer_output was built for {tuple(peer_output.full.shape)} {peer_output.full.dtype} "
+                             f"{peer_output.unit_sizes}, this call needs {want} {ql.dtype} {[s.n_units for s in shards]}")
+        if mine.n_units > 0:
+            attn_fn(ql, kl, vl, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k,
+                    out=peer_output.local_slab(), scatter_to=peer_output.scatter_addresses(), **kwargs)
+        peer_output.sync()
+        return from_units(peer_output.full, B, hq, tensor_layout)
     if mine.n_units > 0:
         o_local = attn_fn(ql, kl, vl, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale, smooth_k=smooth_k,
                           **kwargs)

@@ -116,3 +116,51 @@ def test_context_parallel_ring_on_two_gpus(tmp_path, layout, causal):
     ref = so.sdpa_fp32(q, k, v, tensor_layout=layout, is_causal=causal)
     acc2 = so.accuracy(got.float(), ref)
     assert acc2["cos"] > 0.98 and acc2["max_abs"] < 0.35, acc2
+
+
+def _fused_worker(rank, world, port, layout, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["SAGE_STREAMK"] = "0"
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from sageattention_rdna3_b200 import check_status
+        from sageattention_rdna3_b200.peer_gather import PeerOutput
+        from sageattention_rdna3_b200.shard import plan_shards, sageattn_sharded
+        q, k, v = (t.cuda(rank) for t in _inputs(layout))
+        B, Hq, Hkv, S, D = 2, 6, 3, 700, 128
+        sizes = [s.n_units for s in plan_shards(B, Hq, Hkv, world)]
+        peer = PeerOutput(sizes, (Hq // Hkv, S, D), torch.bfloat16, torch.device("cuda", rank))
+        try:
+            peer.full.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            for _ in range(2):      # twice: the buffers are reused
+                out = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, gather="fused",
+                                       peer_output=peer, kernel="int8")
+            check_status(rank)
+            torch.save(out.cpu(), os.path.join(out_dir, f"fused{rank}.pt"))
+        finally:
+            peer.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+def test_fused_gather_on_two_gpus(tmp_path, monkeypatch, layout):
+    """The attention kernels write their slabs into both GPUs' copies of the output (peer stores from
+    the epilogue); after the one-element all-reduce every rank holds the single-GPU result, bit for
+    bit.  3 + 3 units; a sequence length that is not a multiple of the tile."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_fused_worker, args=(2, _free_port(), layout, str(tmp_path)), nprocs=2, join=True)
+    from sageattention_rdna3_b200 import sageattn
+    monkeypatch.setenv("SAGE_STREAMK", "0")
+    q, k, v = (t.cuda(0) for t in _inputs(layout))
+    want = sageattn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, kernel="int8").cpu()
+    for r in range(2):
+        got = torch.load(os.path.join(str(tmp_path), f"fused{r}.pt"))
+        assert torch.equal(got, want), f"rank {r}"

@@ -110,3 +110,27 @@ def test_unit_slicing_walked_on_one_gpu_is_bit_identical(dev, layout, world):
         H.set_streamk(-1)
     got = from_units(torch.cat(parts, dim=0), B, Hq, layout)
     assert torch.equal(got, whole)
+
+
+@pytest.mark.parametrize("causal,dtype,S,D", [(True, torch.bfloat16, 700, 128), (False, torch.float16, 333, 64)])
+def test_scatter_entry_point_writes_every_copy(dev, causal, dtype, S, D):
+    """sage_qk_int8_sv_f16_attn_scatter on one GPU: the further copies are ordinary local buffers here
+    (on several GPUs they are mapped peer memory); each must equal the primary output bit for bit
+    (sequence lengths that end inside a tile)."""
+    from sageattention_rdna3_b200 import _native, check_status, sageattn
+    B, Hq, Hkv = 2, 4, 2
+    q = H.randn((B, Hq, S, D), 0, dtype).to(dev)
+    k = H.randn((B, Hkv, S, D), 1, dtype, offset=0.5).to(dev)
+    v = H.randn((B, Hkv, S, D), 2, dtype).to(dev)
+    want = sageattn(q, k, v, is_causal=causal, smooth_k=True, kernel="int8")
+    out = torch.empty_like(q)
+    dense = [torch.full_like(q, float("nan")) for _ in range(3)]
+    got = sageattn(q, k, v, is_causal=causal, smooth_k=True, kernel="int8", out=out,
+                   scatter_to=[d.data_ptr() for d in dense])
+    check_status(dev)
+    assert got.data_ptr() == out.data_ptr() and torch.equal(out, want)
+    for i, d in enumerate(dense):
+        assert torch.equal(d, want), f"copy {i}"
+    lib = _native.load_abi()
+    assert lib.sage_qk_int8_sv_f16_attn_scatter(None, None, None, None, 0, 0, 0, None, None, 1, 1, 1, 1, 1, 1, 64, 0, None,
+                                                None, 16, None, None) != 0     # more peers than the kernel takes
