@@ -397,25 +397,6 @@ def measure_gather(prob, steps, warmup, barrier, world, dist, sizes):
 
     res["overlapped_ms"] = timed(overlapped_all, steps, barrier)
 
-    # The gather inside the attention launch: the epilogue writes every finished tile into all ranks'
-    # copies of the output (mapped peer memory, ordinary stores); a one-element all-reduce follows.
-    # Two sets of buffers, used alternately, so that no rank writes into a copy that another rank
-    # may still be reading from the step before.
-    from sageattention_rdna3_b200.peer_gather import PeerOutput
-    peer_sets = [PeerOutput(sizes, unit_shape, prob.o.dtype, dev) for _ in range(2)]
-
-    def fused(i):
-        po = peer_sets[i & 1]
-        if prob.units > 0:
-            prob.step_ops(o=po.local_slab(), peers=po.scatter_addresses())
-        po.sync()
-        finish(po.full)
-
-    for i in range(warmup):
-        fused(i)
-    res["fused_ms"] = timed(fused, steps, barrier)
-    for po in peer_sets:
-        po.close()
     elem = prob.o.element_size()
     per_unit = elem
     for d in unit_shape:
@@ -423,6 +404,36 @@ def measure_gather(prob, steps, warmup, barrier, world, dist, sizes):
     res["recv_bytes_per_rank"] = per_unit * (sum(sizes) - prob.units)
     res["padded"] = padded
     return res
+
+
+def measure_fused_gather(prob, steps, warmup, barrier, dist, sizes):
+    """The gather inside the attention launch: the epilogue writes every finished tile into all ranks'
+    copies of the output (mapped peer memory, ordinary stores); a one-element all-reduce follows.
+    Two sets of buffers, used alternately, so that no rank writes into a copy that another rank may
+    still be reading from the step before.  Returns ms per step, or a string that says why the
+    buffers could not be set up (the same on every rank)."""
+    from sageattention_rdna3_b200.peer_gather import PeerOutput
+    dev, w = prob.dev, prob.w
+    unit_shape = tuple(prob.o.shape[1:])
+    try:
+        peer_sets = [PeerOutput(sizes, unit_shape, prob.o.dtype, dev) for _ in range(2)]
+    except RuntimeError as e:
+        return str(e)
+
+    def fused(i):
+        po = peer_sets[i & 1]
+        if prob.units > 0:
+            prob.step_ops(o=po.local_slab(), peers=po.scatter_addresses())
+        po.sync()
+        if w["layout"] == "NHD":
+            po.full.permute(1, 0, 2, 3).contiguous()
+
+    for i in range(warmup):
+        fused(i)
+    ms = timed(fused, steps, barrier)
+    for po in peer_sets:
+        po.close()
+    return ms
 
 
 def measure_e2e(prob, steps, barrier):
@@ -590,6 +601,9 @@ def main():
         # (4) end to end with host buffers
         if not args.no_e2e:
             e2e = measure_e2e(prob, max(3, min(args.steps, 20)), barrier)
+        # (5) the gather done by the attention kernel (last: it maps other processes' memory)
+        if gather is not None:
+            gather["fused_ms"] = measure_fused_gather(prob, args.steps, args.warmup, barrier, dist, sizes)
     check_status(dev)
 
     def over_ranks(values, op):
@@ -602,7 +616,9 @@ def main():
     g = gather or {}
     ms_public, ms_ops, attn_ms_max, ser_ms, ovl_ms, alone_ms, e2e_ms, floor_ms, fused_ms = over_ranks(
         [ms_public, ms_ops, attn_ms, g.get("serial_ms", 0.0), g.get("overlapped_ms", 0.0), g.get("gather_alone_ms", 0.0),
-         e2e["ms"] if e2e else 0.0, e2e["copy_floor_ms"] if e2e else 0.0, g.get("fused_ms", 0.0)], MAX)
+         e2e["ms"] if e2e else 0.0, e2e["copy_floor_ms"] if e2e else 0.0,
+         g["fused_ms"] if isinstance(g.get("fused_ms"), float) else 0.0], MAX)
+    fused_error = g.get("fused_ms") if isinstance(g.get("fused_ms"), str) else None
     total_nominal, total_executed, h2d_total, d2h_total = over_ranks(
         [prob.nominal, prob.executed, e2e["h2d"] if e2e else 0.0, e2e["d2h"] if e2e else 0.0], SUM)
 
@@ -639,7 +655,8 @@ def main():
                 "serial": {"ms_per_step": ser_ms, "value": tops(ser_ms)},
                 "overlapped": {"ms_per_step": ovl_ms, "value": tops(ovl_ms),
                                "how": "gather of step i on a side stream while step i+1 computes (two output buffers)"},
-                "fused": {"ms_per_step": fused_ms, "value": tops(fused_ms),
+                "fused": {"unavailable": fused_error} if fused_error else {
+                          "ms_per_step": fused_ms, "value": tops(fused_ms),
                           "how": "no gather collective: the attention kernel's epilogue writes every finished tile into "
                                  "all ranks' copies of the output (mapped peer memory, ordinary stores over NVLink), then "
                                  "a one-element all-reduce; one stream, two sets of buffers used alternately"},

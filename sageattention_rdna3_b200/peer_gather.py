@@ -24,6 +24,34 @@ import torch
 from . import _native
 
 
+# One mapping per exported allocation and process, however many buffers live inside it (small
+# buffers of PyTorch's allocator share an allocation): handle -> [mapped base address, users].
+_OPEN = {}
+
+
+def _open(lib, handle: bytes, offset: int):
+    """Address of the peer's buffer in this process, or an error string."""
+    if handle in _OPEN:
+        _OPEN[handle][1] += 1
+        return _OPEN[handle][0] + offset
+    addr = ctypes.c_void_p(0)
+    rc = lib.sage_peer_open(handle, 0, ctypes.byref(addr))
+    if rc != 0:
+        return f"sage_peer_open failed ({rc}): {lib.sage_last_error().decode()}"
+    _OPEN[handle] = [int(addr.value), 1]
+    return int(addr.value) + offset
+
+
+def _close(lib, handle: bytes) -> None:
+    entry = _OPEN.get(handle)
+    if entry is None:
+        return
+    entry[1] -= 1
+    if entry[1] == 0:
+        del _OPEN[handle]
+        _check(lib.sage_peer_close(ctypes.c_void_p(entry[0]), 0), "sage_peer_close")
+
+
 def _check(rc: int, what: str) -> None:
     if rc != 0:
         raise RuntimeError(f"{what} failed ({rc}): {_native.load_abi().sage_last_error().decode()}")
@@ -61,16 +89,28 @@ class PeerOutput:
             mine = (bytes(handle.raw), int(offset.value), tuple(self.full.shape), str(dtype))
             everyone: List[Optional[tuple]] = [None] * self.world
             dist.all_gather_object(everyone, mine, group=group)
-            self._mapped = {}            # rank -> (address of that rank's `full`, offset inside its allocation)
+            self._mapped = {}            # rank -> (address of that rank's `full`, handle of its allocation)
+            problem = None
             for r, (h, off, shape, dt) in enumerate(everyone):
                 if r == self.rank:
                     continue
                 if shape != tuple(self.full.shape) or dt != str(dtype):
-                    raise ValueError(f"rank {r} built a different output buffer: {shape} {dt}")
-                addr = ctypes.c_void_p(0)
-                _check(lib.sage_peer_open(h, off, ctypes.byref(addr)), "sage_peer_open")
-                self._mapped[r] = (int(addr.value), off)
-        dist.barrier(group=group)
+                    problem = f"rank {r} built a different output buffer: {shape} {dt}"
+                    break
+                addr = _open(lib, h, off)
+                if isinstance(addr, str):
+                    problem = f"rank {r}'s buffer: {addr}"
+                    break
+                self._mapped[r] = (addr, h)
+            # all ranks succeed or all ranks raise: nobody is left waiting in a collective
+            verdicts: List[Optional[str]] = [None] * self.world
+            dist.all_gather_object(verdicts, problem, group=group)
+            bad = [f"rank {r}: {v}" for r, v in enumerate(verdicts) if v]
+            if bad:
+                for _, h in self._mapped.values():
+                    _close(lib, h)
+                self._mapped = {}
+                raise RuntimeError("PeerOutput could not be set up: " + "; ".join(bad))
 
     def local_slab(self, rank: Optional[int] = None) -> torch.Tensor:
         """This rank's units inside its own copy (a view: the kernel's ``out``)."""
@@ -94,6 +134,6 @@ class PeerOutput:
         dist.barrier(group=self.group)          # nobody is still writing into a buffer that is about to go
         lib = _native.load_abi()
         with torch.cuda.device(self.full.device):
-            for r, (addr, off) in self._mapped.items():
-                _check(lib.sage_peer_close(ctypes.c_void_p(addr), off), "sage_peer_close")
+            for _, h in self._mapped.values():
+                _close(lib, h)
         self._mapped = {}

@@ -133,18 +133,23 @@ def _fused_worker(rank, world, port, layout, out_dir):
         q, k, v = (t.cuda(rank) for t in _inputs(layout))
         B, Hq, Hkv, S, D = 2, 6, 3, 700, 128
         sizes = [s.n_units for s in plan_shards(B, Hq, Hkv, world)]
-        peer = PeerOutput(sizes, (Hq // Hkv, S, D), torch.bfloat16, torch.device("cuda", rank))
+        # two sets of buffers (small ones share an allocation of the caching allocator: one mapping serves both)
+        peers = [PeerOutput(sizes, (Hq // Hkv, S, D), torch.bfloat16, torch.device("cuda", rank)) for _ in range(2)]
         try:
-            peer.full.fill_(float("nan"))
+            for p in peers:
+                p.full.fill_(float("nan"))
             torch.cuda.synchronize()
             dist.barrier()
-            for _ in range(2):      # twice: the buffers are reused
-                out = sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, gather="fused",
-                                       peer_output=peer, kernel="int8")
+            outs = []
+            for i in range(4):      # the buffers are used alternately and reused
+                outs.append(sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, gather="fused",
+                                             peer_output=peers[i & 1], kernel="int8"))
             check_status(rank)
-            torch.save(out.cpu(), os.path.join(out_dir, f"fused{rank}.pt"))
+            assert torch.equal(outs[2], outs[3])
+            torch.save(outs[3].cpu(), os.path.join(out_dir, f"fused{rank}.pt"))
         finally:
-            peer.close()
+            for p in peers:
+                p.close()
     finally:
         dist.destroy_process_group()
 
