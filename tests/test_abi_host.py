@@ -81,6 +81,20 @@ def test_invalid_arguments_are_rejected_without_cuda():
     rc = lib.sage_quant_qk_int8(ctypes.byref(k), ctypes.byref(k), None, None, None, 0, 1, 2, 2, 16, 16, 64,
                                 ctypes.c_float(0.125), None, None, None, None, None)
     assert rc == 1
+    # scatter: too many peers, a null peer list, a misaligned peer, a peer that is the output itself
+    args = (0x1000, 0x1000, ctypes.byref(v), 0x3000, 1024, 512, 64, 0x4000, 0x5000, 0, 1, 2, 2, 16, 16, 64, 0, None, None)
+    assert lib.sage_qk_int8_sv_f16_attn_scatter(*args, 16, None, None) == 1 and b"n_peers" in lib.sage_last_error()
+    assert lib.sage_qk_int8_sv_f16_attn_scatter(*args, 1, None, None) == 1
+    for bad_peer in (0x7008, 0x3000, 0):
+        peers = (ctypes.c_void_p * 1)(bad_peer)
+        assert lib.sage_qk_int8_sv_f16_attn_scatter(*args, 1, peers, None) == 1, hex(bad_peer)
+        assert b"peer buffer 0" in lib.sage_last_error()
+    # peer mapping: null arguments
+    off = ctypes.c_int64(0)
+    assert lib.sage_peer_export(None, ctypes.create_string_buffer(64), ctypes.byref(off)) == 1
+    assert lib.sage_peer_open(None, 0, ctypes.byref(ctypes.c_void_p(0))) == 1
+    assert lib.sage_peer_open(bytes(64), -16, ctypes.byref(ctypes.c_void_p(0))) == 1
+    assert lib.sage_peer_close(None, 0) == 1
 
 
 def test_graft_entry_build_runs():
