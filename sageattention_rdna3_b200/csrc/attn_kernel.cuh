@@ -810,8 +810,15 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (whole) fence_proxy_async_smem();
       __syncwarp();
+      const bool store_local = whole && q_base + warp * 32 < p.Sq;
+      if (lane == 0 && store_local) {
+#pragma unroll
+        for (int bx = 0; bx < D / 64; ++bx)
+          tma_store_4d(&tm_o, stage + bx * 4096, bx * 64, q_base + warp * 32, hq, b);
+        tma_store_commit();
+      }
       if (!STREAMK && p.n_peers > 0) {
-        // The staged rows go to the peers as well: 8 lanes cover the 128 bytes of one row of a box
+        // The staged rows go to the peers as well, while the TMA reads them for the local copy: 8 lanes cover the 128 bytes of one row of a box
         // (undoing the swizzle), so a warp instruction writes four rows of 128 contiguous bytes.
         const int sub = lane >> 3, piece = lane & 7;
 #pragma unroll
@@ -831,13 +838,7 @@ sage_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
       if (lane == 0) {
-        if (whole && q_base + warp * 32 < p.Sq) {
-#pragma unroll
-          for (int bx = 0; bx < D / 64; ++bx)
-            tma_store_4d(&tm_o, stage + bx * 4096, bx * 64, q_base + warp * 32, hq, b);
-          tma_store_commit();
-          tma_store_wait_read();
-        }
+        if (store_local) tma_store_wait_read();
         if (STREAMK && n_kv > 0) mbar_arrive(epi_done);   // the staging area may be refilled with V
       }
       __syncwarp();

@@ -118,9 +118,11 @@ class PeerOutput:
         return self.full[self.starts[r]:self.starts[r] + self.unit_sizes[r]]
 
     def scatter_addresses(self) -> List[int]:
-        """Where this rank's slab starts in every OTHER rank's copy."""
+        """Where this rank's slab starts in every OTHER rank's copy, nearest higher rank first: the
+        kernel writes a tile to the peers in this order, and no two ranks start with the same one."""
         off = self.starts[self.rank] * self.unit_bytes
-        return [base + off for r, (base, _) in sorted(self._mapped.items())]
+        order = sorted(self._mapped, key=lambda r: (r - self.rank) % self.world)
+        return [self._mapped[r][0] + off for r in order]
 
     def sync(self) -> None:
         """Stream-ordered: returns at once; work queued after it on the current stream sees every
