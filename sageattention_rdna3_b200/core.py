@@ -230,8 +230,9 @@ def sageattn(
             lse = torch.zeros(lse_shape, dtype=torch.float32, device=q.device)
     if q_len == 0 or q_shape[0] == 0 or q_shape[head_dim_idx] == 0:
         o = torch.empty_like(q) if out_arg is None else out_arg
-    elif kv_len == 0 and not scatter_to:
+    elif kv_len == 0:
         # l == 0 for every row -> 0 (csrc/attn_gfx11.cu:771)
+        assert not scatter_to, "scatter_to needs at least one key."
         o = torch.zeros_like(q) if out_arg is None else out_arg.zero_()
     else:
         # core.py:141-198 in one operator call: the un-quantised branch (V as fp16, fp16_attn / bf16_attn)
