@@ -93,6 +93,10 @@ struct AttnParams {
   // gathered output in the memory of the other GPUs of the node.
   int n_peers;
   void* peer_o[kMaxPeers];
+  // Causal, plain launch: 0 = the heaviest (last) query tiles of a head group start first (best
+  // balance), 1 = the lightest first, so that finished tiles - and with them the peer stores - start
+  // flowing early in the launch; the launcher picks 1 when the transfer outlasts the computation.
+  int light_first;
 };
 
 // QKB = bytes per element of Q and K in shared memory: 1 (int8) or 2 (fp16 / bf16, the
@@ -198,7 +202,7 @@ struct SegIter {
       const int g_first = group * p.head_group;
       const int g_size = min(p.head_group, n_bh - g_first);
       const int within = blockIdx.x - group * per_group;
-      const int qt = p.n_q_tiles - 1 - within / g_size;
+      const int qt = p.light_first ? within / g_size : p.n_q_tiles - 1 - within / g_size;
       fill(s, g_first + within % g_size, qt);
       const int kv_limit = CAUSAL ? min(s.q_base + kBlockM, p.Skv) : p.Skv;   // csrc/attn_gfx11.cu:502
       s.kv_lo = 0;
