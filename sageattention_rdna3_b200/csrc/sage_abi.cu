@@ -589,6 +589,7 @@ int sage_qk_int8_sv_f16_attn_scatter(const int8_t* q_i8, const int8_t* k_i8, con
                                      const float* k_scale, int out_dtype, int B, int Hq, int Hkv, int Sq, int Skv,
                                      int D, int is_causal, float* lse, int* status, int n_peers, void* const* peer_o,
                                      void* stream) {
+  static_assert(sage::kMaxPeers == SAGE_MAX_PEERS, "the header and the kernel agree on the number of peers");
   SAGE_REQUIRE(n_peers >= 0 && n_peers <= sage::kMaxPeers, "sage_qk_int8_sv_f16_attn_scatter: n_peers must be 0..%d, got %d",
                sage::kMaxPeers, n_peers);
   SAGE_REQUIRE(n_peers == 0 || peer_o != nullptr, "sage_qk_int8_sv_f16_attn_scatter: null peer list");
