@@ -21,10 +21,10 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _inputs(layout):
+def _inputs(layout, B=2):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from helpers import randn
-    B, Hq, Hkv, S, D = 2, 6, 3, 700, 128
+    Hq, Hkv, S, D = 6, 3, 700, 128
     shp = (lambda h: (B, h, S, D)) if layout == "HND" else (lambda h: (B, S, h, D))
     return randn(shp(Hq), 0, torch.bfloat16), randn(shp(Hkv), 1, torch.bfloat16, offset=1.0), randn(shp(Hkv), 2, torch.bfloat16)
 
@@ -118,7 +118,7 @@ def test_context_parallel_ring_on_two_gpus(tmp_path, layout, causal):
     assert acc2["cos"] > 0.98 and acc2["max_abs"] < 0.35, acc2
 
 
-def _fused_worker(rank, world, port, layout, out_dir):
+def _fused_worker(rank, world, port, layout, B, out_dir):
     sys.path.insert(0, ROOT)
     os.environ["SAGE_STREAMK"] = "0"
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -130,8 +130,8 @@ def _fused_worker(rank, world, port, layout, out_dir):
         from sageattention_rdna3_b200 import check_status
         from sageattention_rdna3_b200.peer_gather import PeerOutput
         from sageattention_rdna3_b200.shard import plan_shards, sageattn_sharded
-        q, k, v = (t.cuda(rank) for t in _inputs(layout))
-        B, Hq, Hkv, S, D = 2, 6, 3, 700, 128
+        q, k, v = (t.cuda(rank) for t in _inputs(layout, B))
+        Hq, Hkv, S, D = 6, 3, 700, 128
         sizes = [s.n_units for s in plan_shards(B, Hq, Hkv, world)]
         # two sets of buffers (small ones share an allocation of the caching allocator: one mapping serves both)
         peers = [PeerOutput(sizes, (Hq // Hkv, S, D), torch.bfloat16, torch.device("cuda", rank)) for _ in range(2)]
@@ -154,17 +154,18 @@ def _fused_worker(rank, world, port, layout, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("layout", ["HND", "NHD"])
-def test_fused_gather_on_two_gpus(tmp_path, monkeypatch, layout):
+@pytest.mark.parametrize("layout,B", [("HND", 2), ("NHD", 2), ("HND", 1)])
+def test_fused_gather_on_two_gpus(tmp_path, monkeypatch, layout, B):
     """The attention kernels write their slabs into both GPUs' copies of the output (peer stores from
     the epilogue); after the one-element all-reduce every rank holds the single-GPU result, bit for
-    bit.  3 + 3 units; a sequence length that is not a multiple of the tile."""
+    bit.  3 + 3 units, or 2 + 1 (slabs of different sizes); a sequence length that is not a multiple
+    of the tile."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    mp.spawn(_fused_worker, args=(2, _free_port(), layout, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_fused_worker, args=(2, _free_port(), layout, B, str(tmp_path)), nprocs=2, join=True)
     from sageattention_rdna3_b200 import sageattn
     monkeypatch.setenv("SAGE_STREAMK", "0")
-    q, k, v = (t.cuda(0) for t in _inputs(layout))
+    q, k, v = (t.cuda(0) for t in _inputs(layout, B))
     want = sageattn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, kernel="int8").cpu()
     for r in range(2):
         got = torch.load(os.path.join(str(tmp_path), f"fused{r}.pt"))
