@@ -162,6 +162,12 @@ int sage_qk_int8_sv_f16_attn_scatter(const int8_t* q_i8, const int8_t* k_i8, con
                                      int D, int is_causal, float* lse, int* status, int n_peers, void* const* peer_o,
                                      void* stream);
 
+/* The same for the un-quantised kernel (sage_direct_attn). */
+int sage_direct_attn_scatter(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                             int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq,
+                             int Hkv, int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status,
+                             int n_peers, void* const* peer_o, void* stream);
+
 /* Mapping of a device buffer that another process of the node owns (one process per GPU).
  * No counterpart in the reference.  sage_peer_export, in the owner: the 64-byte CUDA IPC handle of the
  * allocation that contains `ptr` (memory from cudaMalloc, which is what PyTorch's default allocator

@@ -90,6 +90,9 @@ def load_abi() -> ctypes.CDLL:
     lib.sage_qk_int8_sv_f16_attn_scatter.restype = i
     lib.sage_qk_int8_sv_f16_attn_scatter.argtypes = [vp, vp, sp, vp, i64, i64, i64, vp, vp, i, i, i, i, i, i, i, i, vp,
                                                      vp, i, ctypes.POINTER(vp), vp]
+    lib.sage_direct_attn_scatter.restype = i
+    lib.sage_direct_attn_scatter.argtypes = [sp, sp, sp, vp, i64, i64, i64, i, i, i, i, i, i, i, i, ctypes.c_float, vp, vp,
+                                             i, ctypes.POINTER(vp), vp]
     lib.sage_peer_export.restype = i
     lib.sage_peer_export.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(i64)]
     lib.sage_peer_open.restype = i

@@ -162,7 +162,7 @@ def sageattn(
     Two keywords beyond the reference's, used by the multi-GPU paths: ``out`` (a tensor with the
     shape, dtype and device of ``q``; fp16 / bf16 inputs only) receives the result instead of a new
     tensor, and ``scatter_to`` (device addresses of further copies of ``out``, normally in other
-    GPUs' memory, see :mod:`.peer_gather`; INT8 kernel only) makes the kernel write them as well.
+    GPUs' memory, see :mod:`.peer_gather`) makes the kernel write them as well.
     """
     dtype = q.dtype
     assert q.is_cuda, "Input tensors must be on CUDA/HIP device."
@@ -238,7 +238,6 @@ def sageattn(
         # core.py:141-198 in one operator call: the un-quantised branch (V as fp16, fp16_attn / bf16_attn)
         # or the INT8 branch ([K mean,] quantise Q / K and convert a bf16 V in one launch, attention).
         direct = _pick_direct(kwargs.get("kernel"), headdim, tensor_layout, is_causal, q_len, kv_len)
-        assert not (direct and scatter_to), "scatter_to is served by the INT8 kernel only (pass kernel='int8')."
         smooth = bool(smooth_k) and not direct          # the un-quantised branch has no use for the mean
         if _MIRROR_ON:
             _, seen = _status_mirror(q.device)

@@ -590,12 +590,14 @@ int sage_qk_int8_sv_f16_attn_scatter(const int8_t* q_i8, const int8_t* k_i8, con
                                      int D, int is_causal, float* lse, int* status, int n_peers, void* const* peer_o,
                                      void* stream) {
   static_assert(sage::kMaxPeers == SAGE_MAX_PEERS, "the header and the kernel agree on the number of peers");
-  SAGE_REQUIRE(n_peers >= 0 && n_peers <= sage::kMaxPeers, "sage_qk_int8_sv_f16_attn_scatter: n_peers must be 0..%d, got %d",
-               sage::kMaxPeers, n_peers);
-  SAGE_REQUIRE(n_peers == 0 || peer_o != nullptr, "sage_qk_int8_sv_f16_attn_scatter: null peer list");
-  for (int i = 0; i < n_peers; ++i) {
-    SAGE_REQUIRE(peer_o[i] != nullptr && aligned16(peer_o[i]) && peer_o[i] != o,
-                 "sage_qk_int8_sv_f16_attn_scatter: peer buffer %d must be a 16-byte aligned address other than o", i);
+  {
+    SAGE_REQUIRE(n_peers >= 0 && n_peers <= sage::kMaxPeers, "sage_qk_int8_sv_f16_attn_scatter: n_peers must be 0..%d, got %d",
+                 sage::kMaxPeers, n_peers);
+    SAGE_REQUIRE(n_peers == 0 || peer_o != nullptr, "sage_qk_int8_sv_f16_attn_scatter: null peer list");
+    for (int i = 0; i < n_peers; ++i) {
+      SAGE_REQUIRE(peer_o[i] != nullptr && aligned16(peer_o[i]) && peer_o[i] != o,
+                   "sage_qk_int8_sv_f16_attn_scatter: peer buffer %d must be a 16-byte aligned address other than o", i);
+    }
   }
   return attn_int8_impl(q_i8, k_i8, v16, o, o_stride_b, o_stride_h, o_stride_s, q_scale, k_scale, out_dtype, B, Hq, Hkv,
                         Sq, Skv, D, is_causal, lse, nullptr, status, nullptr, 0, n_peers, peer_o, stream);
@@ -790,10 +792,45 @@ int sage_direct_attn(const sage_strided_t* q, const sage_strided_t* k, const sag
                              sm_scale, lse, status, nullptr, 0, stream);
 }
 
+namespace {
+int check_peers(const char* who, int n_peers, void* const* peer_o, const void* o) {
+  SAGE_REQUIRE(n_peers >= 0 && n_peers <= sage::kMaxPeers, "%s: n_peers must be 0..%d, got %d", who, sage::kMaxPeers, n_peers);
+  SAGE_REQUIRE(n_peers == 0 || peer_o != nullptr, "%s: null peer list", who);
+  for (int i = 0; i < n_peers; ++i) {
+    SAGE_REQUIRE(peer_o[i] != nullptr && aligned16(peer_o[i]) && peer_o[i] != o,
+                 "%s: peer buffer %d must be a 16-byte aligned address other than o", who, i);
+  }
+  return SAGE_OK;
+}
+int direct_attn_impl(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
+                     int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status, void* workspace,
+                     int64_t workspace_bytes, int n_peers, void* const* peer_o, void* stream);
+}  // namespace
+
 int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
                         int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
                         int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status,
                         void* workspace, int64_t workspace_bytes, void* stream) {
+  return direct_attn_impl(q, k, v16, o, o_stride_b, o_stride_h, o_stride_s, dtype, B, Hq, Hkv, Sq, Skv, D, is_causal,
+                          sm_scale, lse, status, workspace, workspace_bytes, 0, nullptr, stream);
+}
+
+int sage_direct_attn_scatter(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                             int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq,
+                             int Hkv, int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status,
+                             int n_peers, void* const* peer_o, void* stream) {
+  const int rc = check_peers("sage_direct_attn_scatter", n_peers, peer_o, o);
+  if (rc) return rc;
+  return direct_attn_impl(q, k, v16, o, o_stride_b, o_stride_h, o_stride_s, dtype, B, Hq, Hkv, Sq, Skv, D, is_causal,
+                          sm_scale, lse, status, nullptr, 0, n_peers, peer_o, stream);
+}
+
+namespace {
+int direct_attn_impl(const sage_strided_t* q, const sage_strided_t* k, const sage_strided_t* v16, void* o,
+                     int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_s, int dtype, int B, int Hq, int Hkv,
+                     int Sq, int Skv, int D, int is_causal, float sm_scale, float* lse, int* status, void* workspace,
+                     int64_t workspace_bytes, int n_peers, void* const* peer_o, void* stream) {
   SAGE_REQUIRE(q && q->ptr && v16 && o, "sage_direct_attn: null pointer");
   SAGE_REQUIRE(Skv == 0 || (k && k->ptr && v16->ptr), "sage_direct_attn: null pointer");
   SAGE_REQUIRE(dtype == SAGE_DTYPE_F16 || dtype == SAGE_DTYPE_BF16, "sage_direct_attn: dtype must be f16 or bf16");
@@ -812,6 +849,8 @@ int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const 
   fill_attn_params(&p, o, o_stride_b, o_stride_h, o_stride_s, dtype, B, Hq, Hkv, Sq, Skv, lse, status);
   p.qk_bf16 = (dtype == SAGE_DTYPE_BF16);
   p.score_scale = sm_scale * 1.4426950408889634f;       // csrc/attn_gfx11.cu:34, as for the quantised path
+  p.n_peers = n_peers;                                  // (short sequences: the order of the items is left alone)
+  for (int i = 0; i < n_peers; ++i) p.peer_o[i] = peer_o[i];
 
   // No keys: nothing is loaded (see sage_qk_int8_sv_f16_attn_lse); the maps describe one dummy row.
   const int skv_map = Skv > 0 ? Skv : 1;
@@ -831,7 +870,7 @@ int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const 
   if (rc) return rc;
   rc = encode_strided_16bit(&to, qk_dt, o, D, Sq, Hq, B, o_stride_s, o_stride_h, o_stride_b, 32, "o");
   if (rc) return rc;
-  if (workspace != nullptr) {
+  if (workspace != nullptr && n_peers == 0) {
     StreamKPlan plan;
     rc = plan_streamk(&plan, B, Hq, Sq, Skv, D, is_causal);
     if (rc) return rc;
@@ -861,5 +900,6 @@ int sage_direct_attn_ws(const sage_strided_t* q, const sage_strided_t* k, const 
   return is_causal ? launch_attn<64, true, false, true>(tq, tk, tv, to, p, st)
                    : launch_attn<64, false, false, true>(tq, tk, tv, to, p, st);
 }
+}  // namespace
 
 }  // extern "C"

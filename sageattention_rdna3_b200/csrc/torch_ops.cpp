@@ -284,7 +284,7 @@ at::Tensor qk_int8_sv_f16_attn(const at::Tensor& q_i8, const at::Tensor& k_i8, c
 at::Tensor direct_attn(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, int64_t layout,
                        int64_t value_layout, int64_t is_causal, double sm_scale, int64_t /*bm_sel*/,
                        const c10::optional<at::Tensor>& status, const c10::optional<at::Tensor>& lse,
-                       at::ScalarType want, const char* name) {
+                       at::ScalarType want, const char* name, at::OptionalIntArrayRef peer_ptrs = c10::nullopt) {
   TORCH_CHECK(q.scalar_type() == want && k.scalar_type() == want && o.scalar_type() == want, name,
               ": query, key and output must be ", want);
   TORCH_CHECK(v.scalar_type() == at::kHalf, name, ": value must be fp16 (convert bf16 with v_to_f16)");
@@ -312,6 +312,16 @@ at::Tensor direct_attn(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   c10::cuda::CUDAGuard guard(q.device());
   const sage_strided_t qs = strided_of(q, layout), ks = strided_of(k, layout), vs = strided_of(v, value_layout);
   const sage_strided_t os = strided_of(o, layout);
+  if (peer_ptrs.has_value() && !peer_ptrs->empty()) {
+    std::vector<void*> peers;
+    for (int64_t a : *peer_ptrs) peers.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(a)));
+    check_rc(sage_direct_attn_scatter(&qs, &ks, &vs, o.data_ptr(), os.stride_b, os.stride_h, os.stride_s, dtype_code(q),
+                                      (int)dq.B, (int)dq.H, (int)dk.H, (int)dq.S, (int)dk.S, (int)dq.D, (int)is_causal,
+                                      (float)sm_scale, lse_ptr, status_ptr, (int)peers.size(), peers.data(),
+                                      current_stream(q)),
+             name);
+    return o;
+  }
   at::Tensor workspace;
   const int64_t ws_bytes = sage_attn_workspace_bytes((int)dq.B, (int)dq.H, (int)dq.S, (int)dk.S, (int)dq.D, (int)is_causal);
   if (ws_bytes > 0) workspace = at::empty({ws_bytes}, q.options().dtype(at::kByte));
@@ -353,15 +363,15 @@ std::vector<at::Tensor> sageattn_fwd(const at::Tensor& q, const at::Tensor& k, c
   } else {
     o = at::empty_like(q);
   }
-  TORCH_CHECK(!(use_direct && peer_ptrs.has_value() && !peer_ptrs->empty()),
-              "peer_ptrs is only served by the INT8 kernel");
+
   const bool bf16 = q.scalar_type() == at::kBFloat16;
   const c10::optional<at::Tensor> st(status), none;
   if (use_direct) {
     if (bf16) {
-      direct_attn(q, k, v_to_f16(v, layout), o, layout, kHND, is_causal, sm_scale, 0, st, lse, at::kBFloat16, "bf16_attn");
+      direct_attn(q, k, v_to_f16(v, layout), o, layout, kHND, is_causal, sm_scale, 0, st, lse, at::kBFloat16, "bf16_attn",
+                  peer_ptrs);
     } else {
-      direct_attn(q, k, v, o, layout, layout, is_causal, sm_scale, 0, st, lse, at::kHalf, "fp16_attn");
+      direct_attn(q, k, v, o, layout, layout, is_causal, sm_scale, 0, st, lse, at::kHalf, "fp16_attn", peer_ptrs);
     }
     return {o};
   }

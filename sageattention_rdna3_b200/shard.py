@@ -89,8 +89,7 @@ def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_l
     ``gather="fused"`` with ``peer_output`` (a :class:`.peer_gather.PeerOutput` built once for these
     shapes): the attention kernel writes this rank's slab into every rank's copy of the output while
     it computes, and the collective shrinks to a one-element all-reduce.  The result is a view of
-    ``peer_output.full`` (valid until the next call that uses the same ``peer_output``).  Calls that
-    the un-quantised kernel serves fall back to the all-gather.
+    ``peer_output.full`` (valid until the next call that uses the same ``peer_output``).
     """
     import torch.distributed as dist
     if attn_fn is None:
@@ -120,7 +119,7 @@ def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_l
         from .core import use_direct_kernel
         direct = use_direct_kernel(q.size(-1), tensor_layout, is_causal, q_len, kv_len)
         kwargs["kernel"] = "direct" if direct else "int8"
-    if gather == "fused" and world > 1 and kwargs["kernel"] == "int8":
+    if gather == "fused" and world > 1:
         if peer_output is None:
             raise ValueError('gather="fused" needs peer_output=PeerOutput(...)')
         rep = hq // hkv

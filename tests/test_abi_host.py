@@ -27,7 +27,7 @@ def test_header_declares_the_expected_entry_points():
                                          "sage_qk_int8_sv_f16_attn_ws", "sage_direct_attn_ws",
                                          "sage_quant_qk_int8_smooth_static", "sage_test_set_wait_limit_us",
                                          "sage_test_drop_v_load", "sage_set_streamk", "sage_prep_smooth_qkv", "sage_prep_smooth_preferred", "sage_fold_attn_partial", "sage_set_status_mirror",
-                                         "sage_qk_int8_sv_f16_attn_scatter", "sage_peer_export", "sage_peer_open",
+                                         "sage_qk_int8_sv_f16_attn_scatter", "sage_direct_attn_scatter", "sage_peer_export", "sage_peer_open",
                                          "sage_peer_close"])
 
 

@@ -118,7 +118,7 @@ def test_context_parallel_ring_on_two_gpus(tmp_path, layout, causal):
     assert acc2["cos"] > 0.98 and acc2["max_abs"] < 0.35, acc2
 
 
-def _fused_worker(rank, world, port, layout, B, out_dir):
+def _fused_worker(rank, world, port, layout, B, kernel, out_dir):
     sys.path.insert(0, ROOT)
     os.environ["SAGE_STREAMK"] = "0"
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -143,7 +143,7 @@ def _fused_worker(rank, world, port, layout, B, out_dir):
             outs = []
             for i in range(4):      # the buffers are used alternately and reused
                 outs.append(sageattn_sharded(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, gather="fused",
-                                             peer_output=peers[i & 1], kernel="int8"))
+                                             peer_output=peers[i & 1], kernel=kernel))
             check_status(rank)
             assert torch.equal(outs[2], outs[3])
             torch.save(outs[3].cpu(), os.path.join(out_dir, f"fused{rank}.pt"))
@@ -154,19 +154,19 @@ def _fused_worker(rank, world, port, layout, B, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("layout,B", [("HND", 2), ("NHD", 2), ("HND", 1)])
-def test_fused_gather_on_two_gpus(tmp_path, monkeypatch, layout, B):
+@pytest.mark.parametrize("layout,B,kernel", [("HND", 2, "int8"), ("NHD", 2, "int8"), ("HND", 1, "int8"), ("NHD", 1, "direct")])
+def test_fused_gather_on_two_gpus(tmp_path, monkeypatch, layout, B, kernel):
     """The attention kernels write their slabs into both GPUs' copies of the output (peer stores from
     the epilogue); after the one-element all-reduce every rank holds the single-GPU result, bit for
     bit.  3 + 3 units, or 2 + 1 (slabs of different sizes); a sequence length that is not a multiple
     of the tile."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    mp.spawn(_fused_worker, args=(2, _free_port(), layout, B, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_fused_worker, args=(2, _free_port(), layout, B, kernel, str(tmp_path)), nprocs=2, join=True)
     from sageattention_rdna3_b200 import sageattn
     monkeypatch.setenv("SAGE_STREAMK", "0")
     q, k, v = (t.cuda(0) for t in _inputs(layout, B))
-    want = sageattn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, kernel="int8").cpu()
+    want = sageattn(q, k, v, tensor_layout=layout, is_causal=True, smooth_k=True, kernel=kernel).cpu()
     for r in range(2):
         got = torch.load(os.path.join(str(tmp_path), f"fused{r}.pt"))
         assert torch.equal(got, want), f"rank {r}"

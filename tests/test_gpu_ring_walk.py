@@ -112,10 +112,11 @@ def test_unit_slicing_walked_on_one_gpu_is_bit_identical(dev, layout, world):
     assert torch.equal(got, whole)
 
 
+@pytest.mark.parametrize("kernel", ["int8", "direct"])
 @pytest.mark.parametrize("causal,dtype,S,D,n_copies", [(True, torch.bfloat16, 700, 128, 3), (False, torch.float16, 333, 64, 3),
                                                         (True, torch.bfloat16, 700, 128, 12)])
-def test_scatter_entry_point_writes_every_copy(dev, causal, dtype, S, D, n_copies):
-    """sage_qk_int8_sv_f16_attn_scatter on one GPU: the further copies are ordinary local buffers here
+def test_scatter_entry_point_writes_every_copy(dev, causal, dtype, S, D, n_copies, kernel):
+    """sage_qk_int8_sv_f16_attn_scatter / sage_direct_attn_scatter on one GPU: the further copies are ordinary local buffers here
     (on several GPUs they are mapped peer memory); each must equal the primary output bit for bit
     (sequence lengths that end inside a tile)."""
     from sageattention_rdna3_b200 import _native, check_status, sageattn
@@ -123,12 +124,12 @@ def test_scatter_entry_point_writes_every_copy(dev, causal, dtype, S, D, n_copie
     q = H.randn((B, Hq, S, D), 0, dtype).to(dev)
     k = H.randn((B, Hkv, S, D), 1, dtype, offset=0.5).to(dev)
     v = H.randn((B, Hkv, S, D), 2, dtype).to(dev)
-    want = sageattn(q, k, v, is_causal=causal, smooth_k=True, kernel="int8")
+    want = sageattn(q, k, v, is_causal=causal, smooth_k=True, kernel=kernel)
     out = torch.empty_like(q)
     # (with 12 copies the transfer is estimated to outlast the computation by a factor in the band in
     # which the launcher starts the causal items lightest first: the results do not depend on the order)
     dense = [torch.full_like(q, float("nan")) for _ in range(n_copies)]
-    got = sageattn(q, k, v, is_causal=causal, smooth_k=True, kernel="int8", out=out,
+    got = sageattn(q, k, v, is_causal=causal, smooth_k=True, kernel=kernel, out=out,
                    scatter_to=[d.data_ptr() for d in dense])
     check_status(dev)
     assert got.data_ptr() == out.data_ptr() and torch.equal(out, want)
