@@ -103,9 +103,9 @@ class PeerOutput:
                     break
                 self._mapped[r] = (addr, h)
             # all ranks succeed or all ranks raise: nobody is left waiting in a collective
-            verdicts: List[Optional[str]] = [None] * self.world
-            dist.all_gather_object(verdicts, problem, group=group)
-            bad = [f"rank {r}: {v}" for r, v in enumerate(verdicts) if v]
+            reports: List[Optional[str]] = [None] * self.world
+            dist.all_gather_object(reports, problem, group=group)
+            bad = [f"rank {r}: {v}" for r, v in enumerate(reports) if v]
             if bad:
                 for _, h in self._mapped.values():
                     _close(lib, h)
