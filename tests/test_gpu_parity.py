@@ -717,3 +717,31 @@ def test_random_ragged_shapes(dev, monkeypatch, case):
     acc = so.accuracy(o.float().cpu(), emu.float())
     assert acc["cos"] >= COS_MIN and acc["rel_l1"] <= REL_L1_MAX, acc
     assert (lse.cpu() - lse_emu).abs().max().item() < 2e-3
+
+
+def test_public_call_can_be_captured_in_a_cuda_graph(dev):
+    """sageattn() never synchronises and allocates only through torch's allocator, so a serving loop
+    with fixed shapes can capture it once and replay it: same bits as the eager call, also after the
+    inputs have been overwritten in place."""
+    from sageattention_rdna3_b200 import check_status, sageattn
+    q = H.randn((2, 4, 1024, 128), 0, torch.bfloat16).to(dev)
+    k = H.randn((2, 2, 1024, 128), 1, torch.bfloat16, offset=0.5).to(dev)
+    v = H.randn((2, 2, 1024, 128), 2, torch.bfloat16).to(dev)
+    call = lambda: sageattn(q, k, v, is_causal=True, smooth_k=True, kernel="int8")
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            call()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = call()
+    graph.replay()
+    torch.cuda.synchronize(dev)
+    assert torch.equal(out, call())
+    q.copy_(H.randn((2, 4, 1024, 128), 7, torch.bfloat16).to(dev))     # new contents, same storage
+    graph.replay()
+    torch.cuda.synchronize(dev)
+    assert torch.equal(out, call())
+    check_status(dev)
