@@ -106,3 +106,45 @@ def test_direct_emulation_against_fp32_sdpa():
         ref = so.sdpa_fp32(q, k, v, tensor_layout=layout, is_causal=causal)
         acc = so.accuracy(o.float(), ref)
         assert o.dtype == dtype and acc["cos"] > 0.9999 and acc["max_abs"] < 2e-2, acc
+
+
+def test_peer_mappings_are_opened_once_per_allocation_and_closed_by_the_last_user():
+    """peer_gather keeps one CUDA-IPC mapping per exported allocation and process: buffers that share
+    an allocation share the mapping, and it is closed when the last of them lets go."""
+    import ctypes
+    from sageattention_rdna3_b200 import peer_gather as pg
+
+    class FakeLib:
+        def __init__(self):
+            self.opened, self.closed, self.fail = [], [], False
+
+        def sage_peer_open(self, handle, offset, out):
+            if self.fail:
+                return 2
+            assert offset == 0                      # the mapping is of the allocation, offsets are added by the caller
+            self.opened.append(handle)
+            ctypes.cast(out, ctypes.POINTER(ctypes.c_void_p))[0] = 0x10000000 + 0x1000000 * len(self.opened)
+            return 0
+
+        def sage_peer_close(self, addr, offset):
+            self.closed.append(addr.value)
+            return 0
+
+        def sage_last_error(self):
+            return b"fake failure"
+
+    lib = FakeLib()
+    pg._OPEN.clear()
+    a = pg._open(lib, b"A" * 64, 256)
+    b = pg._open(lib, b"A" * 64, 4096)              # another buffer in the same allocation
+    c = pg._open(lib, b"B" * 64, 0)
+    assert (a, b, c) == (0x11000000 + 256, 0x11000000 + 4096, 0x12000000)
+    assert lib.opened == [b"A" * 64, b"B" * 64]
+    pg._close(lib, b"A" * 64)
+    assert lib.closed == []                          # still used by the second buffer
+    pg._close(lib, b"A" * 64)
+    pg._close(lib, b"B" * 64)
+    assert lib.closed == [0x11000000, 0x12000000] and pg._OPEN == {}
+    pg._close(lib, b"A" * 64)                        # closing what is not open is a no-op
+    lib.fail = True
+    assert isinstance(pg._open(lib, b"C" * 64, 0), str) and pg._OPEN == {}
